@@ -1,0 +1,139 @@
+// Small memory-bound kernels: test kernel, arena prologue, amax + E4M3 quantisation,
+// SwiGLU, Euler update, type conversion, gathers.
+#pragma once
+
+#include "common.cuh"
+
+// Same signature as the reference's only kernel (tests/vector_add.cu:1-7): out = left + right.
+extern "C" __global__ void vector_add_f32(const float* left, const float* right, float* out, unsigned count) {
+  grid_dependency_wait();
+  const unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < count) out[i] = left[i] + right[i];
+}
+
+// Recipe prologue: set `count` 32-bit words to `value` (the arena is only zeroed once, at
+// session set-up; amax accumulators and status words must restart at zero on every run).
+extern "C" __global__ void agi_fill_u32(unsigned* words, unsigned value, unsigned count) {
+  grid_dependency_wait();
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < count; i += gridDim.x * blockDim.x) words[i] = value;
+}
+
+// amax_bits = max(amax_bits, bits(max |x|)).  Non-negative floats order like their bit
+// patterns, so an integer atomicMax on a zero-initialised word accumulates the maximum.
+extern "C" __global__ void agi_absmax_bf16(const bf16* x, unsigned count, unsigned* amax_bits) {
+  __shared__ float scratch[32];
+  grid_dependency_wait();
+  float best = 0.f;
+  const unsigned vectors = count / 8;
+  const Bf16x8* xv = reinterpret_cast<const Bf16x8*>(x);
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < vectors; i += gridDim.x * blockDim.x) {
+    float f[8];
+    unpack8(xv[i], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) best = fmaxf(best, fabsf(f[j]));
+  }
+  for (unsigned i = vectors * 8 + blockIdx.x * blockDim.x + threadIdx.x; i < count; i += gridDim.x * blockDim.x)
+    best = fmaxf(best, fabsf(__bfloat162float(x[i])));
+  best = block_max(best, scratch);
+  if (threadIdx.x == 0) atomicMax(amax_bits, __float_as_uint(best));
+}
+
+// Per-tensor dynamic quantisation: scale = amax / 448 (1 when amax is 0), q = e4m3(x / scale)
+// with IEEE division and round-to-nearest-even, saturating.  Block 0 publishes `scale`.
+extern "C" __global__ void agi_quantize_e4m3_bf16(const bf16* x, uint8_t* q, const unsigned* amax_bits,
+                                                   float* scale_out, unsigned count) {
+  grid_dependency_wait();
+  const float amax = __uint_as_float(*amax_bits);
+  const float scale = amax > 0.f ? __fdiv_rn(amax, 448.f) : 1.f;
+  if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = scale;
+  const unsigned vectors = count / 8;
+  const Bf16x8* xv = reinterpret_cast<const Bf16x8*>(x);
+  uint2* qv = reinterpret_cast<uint2*>(q);
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < vectors; i += gridDim.x * blockDim.x) {
+    float f[8];
+    unpack8(xv[i], f);
+    unsigned lo = 0, hi = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      lo |= unsigned(float_to_e4m3(__fdiv_rn(f[j], scale))) << (8 * j);
+      hi |= unsigned(float_to_e4m3(__fdiv_rn(f[4 + j], scale))) << (8 * j);
+    }
+    qv[i] = make_uint2(lo, hi);
+  }
+  for (unsigned i = vectors * 8 + blockIdx.x * blockDim.x + threadIdx.x; i < count; i += gridDim.x * blockDim.x)
+    q[i] = float_to_e4m3(__fdiv_rn(__bfloat162float(x[i]), scale));
+}
+
+// out[r, c] = silu(gate[r, c]) * up[r, c]; gate/up may be column blocks of one wider buffer.
+extern "C" __global__ void agi_swiglu_bf16(const bf16* gate, const bf16* up, bf16* out, unsigned rows, unsigned cols,
+                                            unsigned in_stride, unsigned out_stride) {
+  grid_dependency_wait();
+  const unsigned per_row = cols / 8;
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < rows * per_row; i += gridDim.x * blockDim.x) {
+    const unsigned r = i / per_row, c = (i % per_row) * 8;
+    float g[8], u[8];
+    unpack8(*reinterpret_cast<const Bf16x8*>(gate + size_t(r) * in_stride + c), g);
+    unpack8(*reinterpret_cast<const Bf16x8*>(up + size_t(r) * in_stride + c), u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) g[j] = silu(g[j]) * u[j];
+    *reinterpret_cast<Bf16x8*>(out + size_t(r) * out_stride + c) = pack8(g);
+  }
+}
+
+// Flow-matching Euler update on the fp32 action latent: x += dt * v (v is the bf16 velocity);
+// also refreshes the bf16 copy the next step's encoder reads.
+extern "C" __global__ void agi_euler_step(float* x, const bf16* velocity, bf16* x_bf16, float dt, unsigned count) {
+  grid_dependency_wait();
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < count; i += gridDim.x * blockDim.x) {
+    const float next = x[i] + dt * __bfloat162float(velocity[i]);
+    x[i] = next;
+    x_bf16[i] = __float2bfloat16_rn(next);
+  }
+}
+
+extern "C" __global__ void agi_bf16_to_f32(const bf16* in, float* out, unsigned count) {
+  grid_dependency_wait();
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < count; i += gridDim.x * blockDim.x)
+    out[i] = __bfloat162float(in[i]);
+}
+extern "C" __global__ void agi_f32_to_bf16(const float* in, bf16* out, unsigned count) {
+  grid_dependency_wait();
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < count; i += gridDim.x * blockDim.x)
+    out[i] = __float2bfloat16_rn(in[i]);
+}
+
+// Copy `rows` x `cols` bf16 with independent row strides (concatenation, slicing).
+extern "C" __global__ void agi_copy_rows_bf16(const bf16* in, bf16* out, unsigned rows, unsigned cols,
+                                               unsigned in_stride, unsigned out_stride) {
+  grid_dependency_wait();
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < rows * cols; i += gridDim.x * blockDim.x) {
+    const unsigned r = i / cols, c = i % cols;
+    out[size_t(r) * out_stride + c] = in[size_t(r) * in_stride + c];
+  }
+}
+
+// out[r, :] = table[ids[r], :]  (embedding lookup; `cols` a multiple of 8).
+extern "C" __global__ void agi_gather_rows_bf16(const bf16* table, const int* ids, bf16* out, unsigned rows,
+                                                 unsigned cols, unsigned table_rows, unsigned out_stride) {
+  grid_dependency_wait();
+  const unsigned per_row = cols / 8;
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < rows * per_row; i += gridDim.x * blockDim.x) {
+    const unsigned r = i / per_row, c = (i % per_row) * 8;
+    unsigned id = static_cast<unsigned>(ids[r]);
+    if (id >= table_rows) id = table_rows - 1;  // ids are validated offline; clamp instead of faulting
+    *reinterpret_cast<Bf16x8*>(out + size_t(r) * out_stride + c) =
+        *reinterpret_cast<const Bf16x8*>(table + size_t(id) * cols + c);
+  }
+}
+
+// out[r, :] += addend[r % addend_rows, :]  (positional embeddings, broadcast rows).
+extern "C" __global__ void agi_add_rows_bf16(bf16* out, const bf16* addend, unsigned rows, unsigned cols,
+                                              unsigned out_stride, unsigned addend_rows) {
+  grid_dependency_wait();
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < rows * cols; i += gridDim.x * blockDim.x) {
+    const unsigned r = i / cols, c = i % cols;
+    const float sum = __bfloat162float(out[size_t(r) * out_stride + c]) +
+                      __bfloat162float(addend[size_t(r % addend_rows) * cols + c]);
+    out[size_t(r) * out_stride + c] = __float2bfloat16_rn(sum);
+  }
+}

@@ -1,0 +1,7 @@
+// The sm_100a kernel bundle of the AIM artifact set: one translation unit -> one CUBIN.
+//   nvcc -cubin -arch=sm_100a -O3 -o kernels.cubin kernels.cu
+#include "elementwise.cuh"
+#include "norm.cuh"
+#include "rope.cuh"
+#include "attention.cuh"
+#include "gemm_simt.cuh"

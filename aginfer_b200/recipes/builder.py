@@ -1,0 +1,260 @@
+"""Recipe builder: model description -> ``plan.json`` / ``tactics.json`` for the sm100 bundle.
+
+A recipe is the static launch list the loader replays: every kernel, grid, block and
+argument is fixed here, offline.  The builder keeps three address spaces apart, exactly as
+the plan format does (reference ``src/aginfer/plan.py:284-317``):
+
+* profile tensors (caller buffers), referenced by name;
+* the session arena, handed out by a bump allocator with 256-byte alignment; the first
+  ``RESERVED`` bytes hold the status word and the per-run counters the prologue clears;
+* the packed weight blob, whose offsets follow from the checkpoint's tensor names and sizes
+  alone (``weights.weight_layout``), so a plan can be written before the blob exists.
+
+One method per kernel family wraps the launch geometry ("tactic") for that kernel; each
+use is recorded for ``tactics.json``.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Any, Mapping, Sequence
+
+from ..target import CHECKPOINT_DTYPE_BYTES
+from ..weights import weight_layout
+
+ALIGN = 256
+RESERVED = 1024          # bytes at arena offset 0: status word + counters, zeroed every run
+STATUS_WORD = 0          # u32: first error recorded by a kernel (0 = none)
+SM_COUNT = 148
+
+FLAG_BIAS, FLAG_RESIDUAL, FLAG_OUT_F32, FLAG_SCALED = 1, 2, 1 << 8, 1 << 9
+ACT = {None: 0, "gelu_tanh": 1 << 4, "silu": 2 << 4}
+PLAN_DTYPE_BYTES = {"F32": 4, "F16": 2, "BF16": 2, "F8_E4M3": 1, "I32": 4}
+
+
+@dataclass(frozen=True)
+class Tensor:
+    """A profile input or output, by name."""
+    name: str
+
+
+@dataclass(frozen=True)
+class Arena:
+    """A byte offset into the session arena."""
+    offset: int
+
+    def __add__(self, nbytes: int) -> "Arena":
+        return Arena(self.offset + nbytes)
+
+
+@dataclass(frozen=True)
+class Weight:
+    """A checkpoint tensor (plus a byte offset inside it)."""
+    name: str
+    byte_offset: int = 0
+
+    def __add__(self, nbytes: int) -> "Weight":
+        return Weight(self.name, self.byte_offset + nbytes)
+
+
+@dataclass(frozen=True)
+class U32:
+    value: int
+
+
+@dataclass(frozen=True)
+class F32:
+    value: float
+
+
+Pointer = Tensor | Arena | Weight
+
+
+def ceil_div(a: int, b: int) -> int:
+    return -(-a // b)
+
+
+def grid_for(work_items: int, threads: int = 256, cap: int = SM_COUNT * 8) -> int:
+    return max(1, min(cap, ceil_div(work_items, threads)))
+
+
+@dataclass
+class Profile:
+    name: str
+    inputs: list[dict[str, Any]] = field(default_factory=list)
+    outputs: list[dict[str, Any]] = field(default_factory=list)
+    launches: list[dict[str, Any]] = field(default_factory=list)
+    graph_safe: bool = True
+
+
+class RecipeBuilder:
+    def __init__(self, weights: Mapping[str, tuple[str, Sequence[int]]], arch: str = "sm100"):
+        self.arch = arch
+        self.weights = {k: (d, tuple(s)) for k, (d, s) in weights.items()}
+        sizes = {k: math.prod(s) * CHECKPOINT_DTYPE_BYTES[d] for k, (d, s) in self.weights.items()}
+        self.weight_offsets, self.weight_bytes = weight_layout(sizes)
+        self.weight_sizes = sizes
+        self._cursor = RESERVED
+        self._high_water = RESERVED
+        self._counter_cursor = 64          # counters live in [64, RESERVED); [0, 64) is the status area
+        self.profiles: list[Profile] = []
+        self.tactics: dict[tuple[str, str], dict[str, Any]] = {}
+        self._profile: Profile | None = None
+
+    # ---- address spaces -------------------------------------------------------------------
+    def alloc(self, nbytes: int, align: int = ALIGN) -> Arena:
+        at = ceil_div(self._cursor, align) * align
+        self._cursor = at + max(nbytes, 1)
+        self._high_water = max(self._high_water, self._cursor)
+        return Arena(at)
+
+    def mark(self) -> int:
+        return self._cursor
+
+    def release(self, mark: int) -> None:
+        """Give back everything allocated since ``mark`` (stack discipline)."""
+        self._cursor = mark
+
+    def counter(self, words: int = 1) -> Arena:
+        """A zero-at-run-start u32 slot (amax accumulators, flags)."""
+        at = self._counter_cursor
+        self._counter_cursor += 4 * words
+        if self._counter_cursor > RESERVED:
+            raise ValueError("out of per-run counter slots")
+        return Arena(at)
+
+    @property
+    def arena_bytes(self) -> int:
+        return ceil_div(self._high_water, ALIGN) * ALIGN
+
+    # ---- profiles -------------------------------------------------------------------------
+    def begin_profile(self, name: str, inputs: Sequence[dict[str, Any]], outputs: Sequence[dict[str, Any]],
+                      graph_safe: bool = True) -> None:
+        self._profile = Profile(name, [dict(i) for i in inputs], [dict(o) for o in outputs], [], graph_safe)
+        self.profiles.append(self._profile)
+        # prologue: clear status word and counters
+        self.launch("agi_fill_u32", (1, 1, 1), (256, 1, 1), [Arena(0), U32(0), U32(RESERVED // 4)],
+                    op="prologue", algorithm="fill_u32")
+
+    def _encode(self, arg: Any) -> dict[str, Any]:
+        if isinstance(arg, Tensor):
+            return {"tensor": arg.name}
+        if isinstance(arg, Arena):
+            return {"arena_offset": arg.offset}
+        if isinstance(arg, Weight):
+            if arg.name not in self.weight_offsets:
+                raise KeyError(f"recipe references unknown weight {arg.name!r}")
+            if arg.byte_offset >= max(self.weight_sizes[arg.name], 1):
+                raise ValueError(f"offset {arg.byte_offset} is outside weight {arg.name!r}")
+            return {"weights_offset": self.weight_offsets[arg.name] + arg.byte_offset}
+        if isinstance(arg, U32):
+            return {"scalar_u32": int(arg.value)}
+        if isinstance(arg, F32):
+            return {"scalar_f32": float(arg.value)}
+        raise TypeError(f"not a kernel argument: {arg!r}")
+
+    def launch(self, kernel: str, grid: Sequence[int], block: Sequence[int], args: Sequence[Any], *,
+               shared_bytes: int = 0, op: str | None = None, algorithm: str | None = None, **tactic: Any) -> None:
+        assert self._profile is not None, "begin_profile first"
+        self._profile.launches.append({"kernel": kernel, "grid": list(grid), "block": list(block),
+                                       "shared_bytes": shared_bytes, "arguments": [self._encode(a) for a in args]})
+        key = (op or kernel, algorithm or kernel)
+        entry = self.tactics.setdefault(key, {"op": key[0], "algorithm": key[1], "kernel": kernel, "uses": 0, **tactic})
+        entry["uses"] += 1
+
+    # ---- kernel families ------------------------------------------------------------------
+    def vector_add(self, left: Pointer, right: Pointer, out: Pointer, count: int) -> None:
+        self.launch("vector_add_f32", (ceil_div(count, 256), 1, 1), (256, 1, 1), [left, right, out, U32(count)],
+                    op="vector_add")
+
+    def quantize_e4m3(self, x: Pointer, q: Pointer, scale_out: Pointer, count: int) -> None:
+        """amax -> scale = amax / 448 -> q = e4m3(x / scale); two launches sharing one counter."""
+        amax = self.counter()
+        blocks = grid_for(count // 8 + 1, 256, SM_COUNT * 4)
+        self.launch("agi_absmax_bf16", (blocks, 1, 1), (256, 1, 1), [x, U32(count), amax], op="absmax")
+        self.launch("agi_quantize_e4m3_bf16", (blocks, 1, 1), (256, 1, 1), [x, q, amax, scale_out, U32(count)],
+                    op="quantize_e4m3")
+
+    def rmsnorm(self, x: Pointer, gain: Pointer, y: Pointer, rows: int, cols: int, eps: float = 1e-6,
+                x_stride: int | None = None, y_stride: int | None = None) -> None:
+        assert cols % 8 == 0
+        self.launch("agi_rmsnorm_bf16", (rows, 1, 1), (min(1024, max(32, ceil_div(cols // 8, 32) * 32)), 1, 1),
+                    [x, gain, y, U32(rows), U32(cols), U32(x_stride or cols), U32(y_stride or cols), F32(eps)],
+                    op="rmsnorm")
+
+    def layernorm(self, x: Pointer, y: Pointer, rows: int, cols: int, eps: float = 1e-5,
+                  scale: Pointer | None = None, shift: Pointer | None = None,
+                  x_stride: int | None = None, y_stride: int | None = None) -> None:
+        assert cols % 8 == 0 and (scale is None) == (shift is None)
+        dummy = Arena(0)
+        self.launch("agi_layernorm_bf16", (rows, 1, 1), (min(1024, max(32, ceil_div(cols // 8, 32) * 32)), 1, 1),
+                    [x, scale or dummy, shift or dummy, y, U32(rows), U32(cols), U32(x_stride or cols),
+                     U32(y_stride or cols), F32(eps), U32(0 if scale is None else 1)],
+                    op="layernorm_modulate" if scale is not None else "layernorm")
+
+    def rope(self, x: Pointer, rows: int, heads: int, head_dim: int, row_stride: int, theta: float,
+             pos_offset: int = 0) -> None:
+        work = rows * heads * head_dim // 2
+        self.launch("agi_rope_bf16", (grid_for(work), 1, 1), (256, 1, 1),
+                    [x, U32(rows), U32(heads), U32(head_dim), U32(row_stride), F32(math.log2(theta)), U32(pos_offset)],
+                    op="rope")
+
+    def mrope(self, x: Pointer, positions: Pointer, rows: int, heads: int, head_dim: int, row_stride: int,
+              theta: float, sections: Sequence[int]) -> None:
+        assert sum(sections) == head_dim // 2 and len(sections) == 3
+        work = rows * heads * head_dim // 2
+        self.launch("agi_mrope_bf16", (grid_for(work), 1, 1), (256, 1, 1),
+                    [x, positions, U32(rows), U32(heads), U32(head_dim), U32(row_stride), F32(math.log2(theta)),
+                     U32(sections[0]), U32(sections[1])], op="mrope")
+
+    def attention(self, q: Pointer, k: Pointer, v: Pointer, o: Pointer, *, q_rows: int, kv_rows: int, q_heads: int,
+                  kv_heads: int, head_dim: int, q_stride: int, k_stride: int, v_stride: int, o_stride: int,
+                  mask: str = "none", mask_arg: int = 0, scale: float | None = None) -> None:
+        assert head_dim <= 128 and head_dim % 2 == 0 and q_heads % kv_heads == 0
+        mode = {"none": 0, "causal": 1, "block": 2}[mask]
+        self.launch("agi_attention_bf16", (ceil_div(q_rows, 8), q_heads, 1), (256, 1, 1),
+                    [q, k, v, o, U32(q_rows), U32(kv_rows), U32(q_heads), U32(kv_heads), U32(head_dim), U32(q_stride),
+                     U32(k_stride), U32(v_stride), U32(o_stride),
+                     F32(scale if scale is not None else head_dim ** -0.5), U32(mode), U32(mask_arg)],
+                    op=f"attention_{mask}", algorithm="warp_per_row")
+
+    def swiglu(self, gate: Pointer, up: Pointer, out: Pointer, rows: int, cols: int, in_stride: int,
+               out_stride: int | None = None) -> None:
+        assert cols % 8 == 0
+        self.launch("agi_swiglu_bf16", (grid_for(rows * cols // 8), 1, 1), (256, 1, 1),
+                    [gate, up, out, U32(rows), U32(cols), U32(in_stride), U32(out_stride or cols)], op="swiglu")
+
+    def gemm(self, x: Pointer, w: Pointer, y: Pointer, M: int, N: int, K: int, *, dtype: str = "bf16",
+             bias: Pointer | None = None, residual: Pointer | None = None, act: str | None = None,
+             scale_a: Pointer | None = None, scale_w: Pointer | None = None, ldx: int | None = None,
+             ldy: int | None = None, out_f32: bool = False, tactic: str = "simt") -> None:
+        """Y[M, N] = epilogue(X[M, K] . W[N, K]^T); ``dtype`` names the operand type (bf16 or e4m3)."""
+        flags = ACT[act] | (FLAG_BIAS if bias else 0) | (FLAG_RESIDUAL if residual else 0) | \
+            (FLAG_OUT_F32 if out_f32 else 0) | (FLAG_SCALED if scale_a else 0)
+        assert (scale_a is None) == (scale_w is None)
+        dummy = Arena(0)
+        args = [x, w, y, bias or dummy, residual or dummy, scale_a or dummy, scale_w or dummy, U32(M), U32(N), U32(K),
+                U32(ldx or K), U32(ldy or N), U32(flags)]
+        if tactic == "simt":
+            self.launch(f"agi_gemm_simt_{dtype}", (ceil_div(N, 64), ceil_div(M, 64), 1), (256, 1, 1), args,
+                        op=f"gemm_{dtype}", algorithm="simt_64x64x16")
+            return
+        raise ValueError(f"unknown GEMM tactic {tactic!r}")
+
+    # ---- outputs --------------------------------------------------------------------------
+    def plan(self) -> dict[str, Any]:
+        return {
+            "cuda_arch": self.arch,
+            "arena_bytes": self.arena_bytes,
+            "workspace_bytes": 0,
+            "shape_dispatch": [{"profile": p.name, "inputs": p.inputs, "outputs": p.outputs, "launches": p.launches}
+                               for p in self.profiles],
+            "cuda_graph_templates": [{"profile": p.name} for p in self.profiles if p.graph_safe],
+        }
+
+    def tactic_database(self) -> dict[str, Any]:
+        return {"cuda_arch": self.arch, "tactics": sorted(self.tactics.values(), key=lambda t: (t["op"], t["algorithm"]))}
+
+
+def io(name: str, dtype: str, shape: Sequence[int]) -> dict[str, Any]:
+    return {"name": name, "dtype": dtype, "shape": list(shape)}

@@ -1,0 +1,181 @@
+"""Parity of each kernel family with the CPU oracle, launched through the packaged recipe path:
+modelc compile -> AIM -> C ABI loader -> cuLaunchKernel from the CUBIN."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+from aginfer_b200.recipes import Tensor, Weight
+from oracle import ops
+from tests.gpu_util import MAX_REL, run_recipe
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+def randn(*shape, seed=0, std=1.0, dtype=BF):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * std).to(dtype)
+
+
+def test_vector_add_through_the_whole_pipeline(tmp_path):
+    # the reference's own GPU test (tests/cuda_runtime_test.cc:50-76): 16 floats, exact to 1e-6
+    left = torch.arange(16, dtype=torch.float32) * 0.5
+    right = torch.arange(16, dtype=torch.float32) * -0.25
+    got, stats = run_recipe(tmp_path, {}, {"left": left, "right": right}, {"output": (torch.float32, (16,))},
+                            lambda r: r.vector_add(Tensor("left"), Tensor("right"), Tensor("output"), 16), repeats=3)
+    assert torch.allclose(got["output"], left + right, atol=1e-6)
+    assert stats["enqueues"] == 3 and stats["graph_launches"] == 3 and stats["graphs_built"] == 1
+    assert stats["kernel_launches"] == stats["launches_per_enqueue"] == 2  # prologue + kernel, captured once
+
+
+def test_plain_launch_mode_matches_graph_mode(tmp_path):
+    from aginfer_b200.runtime import NO_GRAPH_REPLAY
+    left, right = torch.ones(16), torch.full((16,), 2.0)
+    got, stats = run_recipe(tmp_path, {}, {"left": left, "right": right}, {"output": (torch.float32, (16,))},
+                            lambda r: r.vector_add(Tensor("left"), Tensor("right"), Tensor("output"), 16),
+                            flags=NO_GRAPH_REPLAY, repeats=2)
+    assert torch.equal(got["output"], torch.full((16,), 3.0))
+    assert stats["graph_launches"] == 0 and stats["kernel_launches"] == 4
+
+
+@pytest.mark.parametrize("shape", [(1, 2048), (17, 1536), (288, 2048), (3, 1000), (1024, 11008)])
+def test_quantize_e4m3_is_bit_exact(tmp_path, shape):
+    x = randn(*shape, seed=1)
+    want_q, want_s = ops.quantize_e4m3(x)
+    n = x.numel()
+
+    def body(r):
+        r.quantize_e4m3(Tensor("x"), Tensor("q"), Tensor("scale"), n)
+
+    got, _ = run_recipe(tmp_path, {}, {"x": x}, {"q": (torch.float8_e4m3fn, shape), "scale": (torch.float32, (1,))},
+                        body, repeats=2)
+    assert got["scale"].view(torch.int32).item() == want_s.view(torch.int32).item()
+    assert torch.equal(got["q"].view(torch.uint8), want_q.view(torch.uint8))
+
+
+def test_quantize_all_zero_input(tmp_path):
+    x = torch.zeros(4, 64, dtype=BF)
+    got, _ = run_recipe(tmp_path, {}, {"x": x}, {"q": (torch.float8_e4m3fn, (4, 64)), "scale": (torch.float32, (1,))},
+                        lambda r: r.quantize_e4m3(Tensor("x"), Tensor("q"), Tensor("scale"), 256))
+    assert got["scale"].item() == 1.0 and int(got["q"].view(torch.uint8).max()) == 0
+
+
+@pytest.mark.parametrize("rows,cols", [(288, 2048), (17, 1536), (5, 1280), (2, 3584)])
+def test_rmsnorm(tmp_path, rows, cols):
+    x, gain = randn(rows, cols, seed=2), (1 + randn(cols, seed=3, std=0.1).float()).to(BF)
+    got, _ = run_recipe(tmp_path, {"norm.weight": gain}, {"x": x}, {"y": (BF, (rows, cols))},
+                        lambda r: r.rmsnorm(Tensor("x"), Weight("norm.weight"), Tensor("y"), rows, cols, 1e-6))
+    assert ops.max_rel_err(got["y"], ops.rmsnorm(x, gain, 1e-6)) < 1e-2
+
+
+@pytest.mark.parametrize("modulated", [False, True])
+def test_layernorm_and_adaln_modulation(tmp_path, modulated):
+    rows, cols = 17, 1536
+    x = (randn(rows, cols, seed=4).float() * 3 + 1.5).to(BF)
+    mod = randn(2 * cols, seed=5, std=0.3)
+
+    def body(r):
+        if modulated:
+            r.layernorm(Tensor("x"), Tensor("y"), rows, cols, 1e-5, scale=Weight("mod"), shift=Weight("mod") + 2 * cols)
+        else:
+            r.layernorm(Tensor("x"), Tensor("y"), rows, cols, 1e-5)
+
+    got, _ = run_recipe(tmp_path, {"mod": mod}, {"x": x}, {"y": (BF, (rows, cols))}, body)
+    want = ops.layernorm(x, 1e-5, mod[:cols], mod[cols:]) if modulated else ops.layernorm(x, 1e-5)
+    assert ops.max_rel_err(got["y"], want) < 1e-2
+
+
+def test_rope_1d(tmp_path):
+    rows, heads, d = 288, 18, 128  # 16 query + 2 key heads rotated, 2 value heads untouched
+    x = randn(rows, (heads + 2) * d, seed=6)
+    from aginfer_b200.recipes import U32
+    width = x.shape[1]
+
+    def body(r):
+        r.launch("agi_copy_rows_bf16", (592, 1, 1), (256, 1, 1),
+                 [Tensor("x"), Tensor("y"), U32(rows), U32(width), U32(width), U32(width)])
+        r.rope(Tensor("y"), rows, heads, d, width, 1e6)
+
+    got, _ = run_recipe(tmp_path, {}, {"x": x}, {"y": (BF, x.shape)}, body)
+    want = x.clone().view(rows, heads + 2, d)
+    want[:, :heads] = ops.rope(want[:, :heads], 1e6)
+    assert torch.equal(got["y"].view(rows, heads + 2, d)[:, heads:], x.view(rows, heads + 2, d)[:, heads:])
+    assert ops.max_rel_err(got["y"], want.view(rows, -1)) < 1e-2
+
+
+def test_mrope_sections(tmp_path):
+    from aginfer_b200.recipes import U32
+    rows, heads, d = 64, 4, 128
+    x = randn(rows, heads * d, seed=7)
+    g = torch.Generator().manual_seed(8)
+    pos = torch.randint(0, 300, (3, rows), generator=g, dtype=torch.int32)
+
+    def body(r):
+        r.launch("agi_copy_rows_bf16", (128, 1, 1), (256, 1, 1),
+                 [Tensor("x"), Tensor("y"), U32(rows), U32(heads * d), U32(heads * d), U32(heads * d)])
+        r.mrope(Tensor("y"), Tensor("pos"), rows, heads, d, heads * d, 1e6, (16, 24, 24))
+
+    got, _ = run_recipe(tmp_path, {}, {"x": x, "pos": pos}, {"y": (BF, x.shape)}, body)
+    want = ops.mrope(x.view(rows, heads, d), pos, 1e6, (16, 24, 24)).view(rows, -1)
+    assert ops.max_rel_err(got["y"], want) < 1e-2
+
+
+ATTENTION_CASES = [
+    # q_rows, kv_rows, q_heads, kv_heads, head_dim, mask, mask_arg
+    (288, 288, 16, 2, 128, "causal", 0),      # decoder layer, GQA causal
+    (17, 17, 32, 32, 48, "none", 0),          # DiT self attention
+    (17, 300, 32, 32, 48, "none", 0),         # DiT cross attention
+    (512, 512, 16, 16, 80, "block", 64),      # vision window attention
+    (512, 512, 16, 16, 80, "block", 256),     # vision full attention, per image
+    (50, 306, 8, 4, 128, "causal", 256),      # action expert over [prefix | suffix]
+    (5, 3, 2, 1, 16, "none", 0),              # ragged, smaller than one tile
+]
+
+
+@pytest.mark.parametrize("case", ATTENTION_CASES, ids=lambda c: "x".join(map(str, c)))
+def test_attention(tmp_path, case):
+    sq, skv, hq, hkv, d, mask, arg = case
+    q, k, v = randn(sq, hq * d, seed=9), randn(skv, hkv * d, seed=10), randn(skv, hkv * d, seed=11)
+    got, _ = run_recipe(tmp_path, {}, {"q": q, "k": k, "v": v}, {"o": (BF, (sq, hq * d))}, lambda r: r.attention(
+        Tensor("q"), Tensor("k"), Tensor("v"), Tensor("o"), q_rows=sq, kv_rows=skv, q_heads=hq, kv_heads=hkv,
+        head_dim=d, q_stride=hq * d, k_stride=hkv * d, v_stride=hkv * d, o_stride=hq * d, mask=mask, mask_arg=arg))
+    want = ops.attention(q.view(sq, hq, d), k.view(skv, hkv, d), v.view(skv, hkv, d), mask=mask, mask_arg=arg)
+    assert ops.max_rel_err(got["o"], want.reshape(sq, -1)) < MAX_REL
+
+
+def test_swiglu(tmp_path):
+    rows, inter = 33, 11008
+    gu = randn(rows, 2 * inter, seed=12)
+    got, _ = run_recipe(tmp_path, {}, {"gu": gu}, {"h": (BF, (rows, inter))}, lambda r: r.swiglu(
+        Tensor("gu"), Tensor("gu"), Tensor("h"), rows, inter, 2 * inter))
+    # gate == up pointer here (same column block); the strided form is covered by the layer test
+    assert ops.max_rel_err(got["h"], ops.swiglu(gu[:, :inter], gu[:, :inter])) < 1e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(17, 1536, 1536), (288, 2560, 2048), (1, 64, 96), (70, 100, 40)])
+def test_gemm_simt_bf16(tmp_path, M, N, K):
+    x, w = randn(M, K, seed=13), randn(N, K, seed=14, std=0.02)
+    bias, res = randn(N, seed=15, std=0.1), randn(M, N, seed=16)
+    got, _ = run_recipe(tmp_path, {"w": w, "b": bias}, {"x": x, "res": res}, {"y": (BF, (M, N))}, lambda r: r.gemm(
+        Tensor("x"), Weight("w"), Tensor("y"), M, N, K, bias=Weight("b"), residual=Tensor("res"), act="gelu_tanh"))
+    want = ops.gemm(x, w, bias=bias, residual=res, act="gelu_tanh")
+    assert ops.max_rel_err(got["y"], want) < MAX_REL
+
+
+def test_gemm_simt_e4m3_scaled(tmp_path):
+    M, N, K = 16, 2048, 2048
+    x, wf = randn(M, K, seed=1), randn(N, K, seed=17, std=0.02)
+    wq, ws = ops.quantize_e4m3(wf)
+    xq, xs = ops.quantize_e4m3(x)
+
+    def body(r):
+        q, s = r.alloc(M * K), r.alloc(4)
+        r.quantize_e4m3(Tensor("x"), q, s, M * K)
+        r.gemm(q, Weight("w"), Tensor("y"), M, N, K, dtype="e4m3", scale_a=s, scale_w=Weight("w_scale"))
+
+    got, _ = run_recipe(tmp_path, {"w": wq, "w_scale": ws.reshape(())}, {"x": x}, {"y": (BF, (M, N))}, body)
+    want = ops.gemm(xq, wq, scale_a=xs, scale_w=ws)
+    assert ops.max_rel_err(got["y"], want) < 1e-2
+    # and the quantised product stays close to the unquantised one
+    assert ops.max_rel_err(got["y"], ops.gemm(x, wf.to(BF))) < 0.1
