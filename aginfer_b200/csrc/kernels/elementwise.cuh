@@ -18,6 +18,12 @@ extern "C" __global__ void agi_fill_u32(unsigned* words, unsigned value, unsigne
   for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < count; i += gridDim.x * blockDim.x) words[i] = value;
 }
 
+// Copy 32-bit words (e.g. the arena's status word into a caller-visible tensor).
+extern "C" __global__ void agi_copy_u32(const unsigned* in, unsigned* out, unsigned count) {
+  grid_dependency_wait();
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < count; i += gridDim.x * blockDim.x) out[i] = in[i];
+}
+
 // amax_bits = max(amax_bits, bits(max |x|)).  Non-negative floats order like their bit
 // patterns, so an integer atomicMax on a zero-initialised word accumulates the maximum.
 extern "C" __global__ void agi_absmax_bf16(const bf16* x, unsigned count, unsigned* amax_bits) {

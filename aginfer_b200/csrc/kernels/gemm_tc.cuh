@@ -1,0 +1,315 @@
+// Tensor-core GEMM for sm_100a: Y[M, N] = epilogue(X[M, K] . W[N, K]^T), bf16 or E4M3 operands,
+// fp32 accumulation in tensor memory (TMEM) with tcgen05.mma.
+//
+// Orientation.  The weight matrix is the MMA's A operand: a CTA owns 128 consecutive rows of
+// W (128 output features) and `TN` tokens, TN a multiple of 16 up to 256.  The accumulator
+// tile D[128 x TN] has one output feature per TMEM lane and one token per column.  This way
+// a batch-1 action head (17 or 50 tokens) and a 1024-token prefill run the same code: few
+// tokens only make the tile narrower, the 128-row weight stream per CTA stays the same.
+//
+// Data movement.  W is checkpoint bytes, [N, K] row-major, i.e. already K-major.  The kernel
+// ABI passes only pointers and scalars, so no tensor-map object can be handed to the kernel;
+// tiles are brought in with 16-byte cp.async copies into the 128-byte-swizzled K-major
+// layout tcgen05 reads (row r, 16-byte chunk c stored at chunk c ^ (r & 7)).  Four producer
+// warps fill a ring of `stages` slots; one thread issues the MMAs; a slot is released by
+// tcgen05.commit.  After the main loop the producer warps become the epilogue: each reads
+// its 32 TMEM lanes with tcgen05.ld and writes bf16 (or fp32) rows.
+//
+// Split-K.  grid.z > 1 slices K.  Each slice adds its partial tile into an fp32 scratch
+// matrix with red.global.add; a per-tile arrival counter elects the last slice, which
+// applies the epilogue, writes Y and leaves scratch and counter zeroed for the next launch.
+// Nobody spins on another CTA.
+//
+// Every wait on an mbarrier is bounded; on expiry the kernel records a code in `status`
+// and carries on with whatever data it has, so a logic error shows up as a status word and
+// wrong numbers, never as a hang.
+#pragma once
+
+#include "common.cuh"
+#include "gemm_simt.cuh"  // gemm_store
+
+namespace tc {
+
+constexpr unsigned kTileN = 128;          // weight rows per CTA (MMA M)
+constexpr unsigned kRowBytes = 128;       // K bytes per row per stage (one swizzle atom)
+constexpr unsigned kATileBytes = kTileN * kRowBytes;
+constexpr unsigned kProducers = 128;
+constexpr unsigned kThreads = 160;        // 4 producer/epilogue warps + 1 MMA warp
+constexpr unsigned kMaxStages = 12;
+constexpr int kLag = 2;                   // a stage is published two commits after it was issued
+constexpr unsigned kSpinLimit = 1u << 22;
+
+enum Status : unsigned { kOkStatus = 0, kTimeoutFull = 0x100, kTimeoutEmpty = 0x200, kTimeoutAccum = 0x300 };
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+  asm volatile("{ .reg .b64 t; mbarrier.arrive.shared::cta.b64 t, [%0]; }" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(unsigned long long* bar, unsigned parity) {
+  unsigned done;
+  asm volatile(
+      "{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// Bounded wait; on expiry writes `code` to the status word once and returns false.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, unsigned* status, unsigned code) {
+  for (unsigned spin = 0; spin < kSpinLimit; ++spin) {
+    if (mbar_test(bar, parity)) return true;
+    if (spin > 64) __nanosleep(32);
+  }
+  atomicCAS(status, 0u, code);
+  return false;
+}
+
+__device__ __forceinline__ void cp_async_16(unsigned dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+// Make this thread's completed shared-memory writes visible to the tensor core's (async proxy) reads.
+__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(unsigned* slot, unsigned columns) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(columns) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_free(unsigned base, unsigned columns) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(unsigned long long* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major, 128-byte swizzle, rows 128 B apart, 8-row groups
+// 1024 B apart (stride byte offset), leading byte offset 1 (unused for swizzled K-major),
+// descriptor version 1, layout type 2 (SWIZZLE_128B) in bits 61-63.
+__device__ __forceinline__ unsigned long long smem_descriptor(unsigned addr) {
+  return (unsigned long long)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor: fp32 accumulate, A and B both K-major, M = 128, N = tokens.
+// kind::f16 -> a/b format 1 (bf16); kind::f8f6f4 -> a/b format 0 (E4M3).
+template <bool kFp8>
+__device__ __forceinline__ unsigned instr_descriptor(unsigned tokens) {
+  const unsigned fmt = kFp8 ? 0u : 1u;
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | ((tokens >> 3) << 17) | ((kTileN >> 4) << 24);
+}
+template <bool kFp8>
+__device__ __forceinline__ void mma(unsigned tmem_d, unsigned long long a, unsigned long long b, unsigned idesc,
+                                    unsigned accumulate) {
+  if (kFp8) {
+    asm volatile(
+        "{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p; }" ::"r"(tmem_d),
+        "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }" ::"r"(tmem_d),
+        "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+// 16 consecutive fp32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_load16(unsigned addr, float v[16]) {
+  unsigned r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(addr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ unsigned tmem_columns_for(unsigned tokens) {
+  unsigned c = 32;
+  while (c < tokens) c <<= 1;
+  return c;
+}
+
+// grid = (ceil(N / 128), ceil(M / TN), splits), block = 160 threads,
+// dynamic shared memory = stages * (16384 + TN * 128) + 1024.
+template <bool kFp8>
+__device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, void* y, const bf16* bias,
+                                          const bf16* residual, const float* scale_a, const float* scale_w,
+                                          float* partial, unsigned* counters, unsigned* status, unsigned M,
+                                          unsigned N, unsigned K, unsigned ldx, unsigned ldy, unsigned flags,
+                                          unsigned TN, unsigned stages) {
+  extern __shared__ unsigned char dynamic_smem[];
+  __shared__ __align__(8) unsigned long long full_bar[kMaxStages];
+  __shared__ __align__(8) unsigned long long empty_bar[kMaxStages];
+  __shared__ __align__(8) unsigned long long accum_bar;
+  __shared__ unsigned tmem_slot;
+  __shared__ unsigned last_flag;
+
+  const unsigned tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const unsigned elem = kFp8 ? 1u : 2u;
+  const unsigned n0 = blockIdx.x * kTileN, m0 = blockIdx.y * TN;
+  const unsigned splits = gridDim.z, split = blockIdx.z;
+  const unsigned k_blocks_total = (K * elem) / kRowBytes;
+  const unsigned per_split = (k_blocks_total + splits - 1) / splits;
+  const unsigned kb_begin = min(split * per_split, k_blocks_total);
+  const unsigned kb_end = min(kb_begin + per_split, k_blocks_total);
+  const unsigned nkb = kb_end - kb_begin;
+  const unsigned stage_bytes = kATileBytes + TN * kRowBytes;
+  const unsigned ring = (smem_u32(dynamic_smem) + 1023u) & ~1023u;  // tiles need 1024-byte alignment
+  const unsigned columns = tmem_columns_for(TN);
+  if (stages > kMaxStages) stages = kMaxStages;
+
+  if (tid == 0) {
+    for (unsigned s = 0; s < stages; ++s) {
+      mbar_init(&full_bar[s], kProducers);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&accum_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 4) tmem_alloc(&tmem_slot, columns);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem_base = tmem_slot;
+
+  grid_dependency_wait();
+  grid_dependency_release();
+
+  if (warp < 4) {
+    // ---------------- producers ----------------
+    const size_t w_row_bytes = size_t(K) * elem, x_row_bytes = size_t(ldx) * elem;
+    const unsigned b_chunks = TN * 8;
+    for (unsigned i = 0; i < nkb + kLag; ++i) {
+      if (i < nkb) {
+        const unsigned s = i % stages, round = i / stages;
+        if (round > 0) mbar_wait(&empty_bar[s], (round - 1) & 1, status, kTimeoutEmpty | s);
+        const size_t k_byte = size_t(kb_begin + i) * kRowBytes;
+        const unsigned a_base = ring + s * stage_bytes, b_base = a_base + kATileBytes;
+#pragma unroll
+        for (unsigned j = 0; j < 8; ++j) {
+          const unsigned idx = tid + j * kProducers, r = idx >> 3, c = idx & 7;
+          const unsigned row = min(n0 + r, N - 1);  // rows past N are loaded from the last row and never stored
+          cp_async_16(a_base + r * kRowBytes + ((c ^ (r & 7)) << 4), w + row * w_row_bytes + k_byte + (c << 4));
+        }
+        for (unsigned idx = tid; idx < b_chunks; idx += kProducers) {
+          const unsigned r = idx >> 3, c = idx & 7;
+          const unsigned row = min(m0 + r, M - 1);
+          cp_async_16(b_base + r * kRowBytes + ((c ^ (r & 7)) << 4), x + row * x_row_bytes + k_byte + (c << 4));
+        }
+      }
+      cp_async_commit();  // an empty group past the end keeps the wait arithmetic uniform
+      if (i >= kLag) {
+        cp_async_wait<kLag>();
+        fence_async_shared();
+        mbar_arrive(&full_bar[(i - kLag) % stages]);
+      }
+    }
+  } else {
+    // ---------------- MMA warp: every lane waits, lane 0 issues ----------------
+    const unsigned idesc = instr_descriptor<kFp8>(TN);
+    for (unsigned i = 0; i < nkb; ++i) {
+      const unsigned s = i % stages, round = i / stages;
+      mbar_wait(&full_bar[s], round & 1, status, kTimeoutFull | s);
+      tc_fence_after();
+      if (lane == 0) {
+        const unsigned a_base = ring + s * stage_bytes, b_base = a_base + kATileBytes;
+        const unsigned long long a_desc = smem_descriptor(a_base), b_desc = smem_descriptor(b_base);
+#pragma unroll
+        for (unsigned k = 0; k < 4; ++k)  // 4 x 32 bytes of K per stage; +2 advances the start address by 32 B
+          mma<kFp8>(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (i | k) != 0);
+        tc_commit(&empty_bar[s]);
+      }
+      __syncwarp();
+    }
+    if (lane == 0) tc_commit(&accum_bar);
+    __syncwarp();
+  }
+
+  // ---------------- epilogue (warps 0-3: TMEM lanes 32 * warp ... +31) ----------------
+  if (warp < 4) {
+    if (nkb > 0) mbar_wait(&accum_bar, 0, status, kTimeoutAccum);
+    tc_fence_after();
+    const unsigned n = n0 + warp * 32 + lane;
+    const float alpha = (flags & kFlagScaled) ? (*scale_a) * (*scale_w) : 1.f;
+    const unsigned lane_addr = tmem_base + ((warp * 32u) << 16);
+    for (unsigned c0 = 0; c0 < TN; c0 += 16) {
+      float v[16];
+      if (nkb > 0) {
+        tmem_load16(lane_addr + c0, v);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = 0.f;
+      }
+      if (n < N) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const unsigned m = m0 + c0 + i;
+          if (m >= M) continue;
+          if (splits == 1) gemm_store(v[i], m, n, y, ldy, bias, residual, alpha, flags);
+          else atomicAdd(partial + size_t(m) * N + n, v[i]);
+        }
+      }
+    }
+    if (splits > 1) __threadfence();  // partial sums ordered before this CTA's arrival count
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_free(tmem_base, columns);
+  }
+  if (splits == 1) return;
+
+  // ---------------- split-K: the last slice to arrive finishes the tile ----------------
+  const unsigned tile = blockIdx.y * gridDim.x + blockIdx.x;
+  if (tid == 0) {
+    __threadfence();
+    last_flag = atomicAdd(&counters[tile], 1u) == splits - 1;
+  }
+  __syncthreads();
+  if (!last_flag) return;
+  __threadfence();
+  if (warp < 4) {
+    const unsigned n = n0 + warp * 32 + lane;
+    const float alpha = (flags & kFlagScaled) ? (*scale_a) * (*scale_w) : 1.f;
+    if (n < N) {
+      for (unsigned i = 0; i < TN; ++i) {
+        const unsigned m = m0 + i;
+        if (m >= M) break;
+        float* cell = partial + size_t(m) * N + n;
+        const float total = __ldcg(cell);
+        *cell = 0.f;  // scratch is handed back zeroed
+        gemm_store(total, m, n, y, ldy, bias, residual, alpha, flags);
+      }
+    }
+  }
+  if (tid == 0) counters[tile] = 0;
+}
+
+}  // namespace tc
+
+extern "C" __global__ void __launch_bounds__(tc::kThreads, 1)
+agi_gemm_tc_bf16(const bf16* x, const bf16* w, void* y, const bf16* bias, const bf16* residual, const float* scale_a,
+                 const float* scale_w, float* partial, unsigned* counters, unsigned* status, unsigned M, unsigned N,
+                 unsigned K, unsigned ldx, unsigned ldy, unsigned flags, unsigned TN, unsigned stages) {
+  tc::gemm_body<false>(reinterpret_cast<const uint8_t*>(x), reinterpret_cast<const uint8_t*>(w), y, bias, residual,
+                       scale_a, scale_w, partial, counters, status, M, N, K, ldx, ldy, flags, TN, stages);
+}
+
+extern "C" __global__ void __launch_bounds__(tc::kThreads, 1)
+agi_gemm_tc_e4m3(const uint8_t* x, const uint8_t* w, void* y, const bf16* bias, const bf16* residual,
+                 const float* scale_a, const float* scale_w, float* partial, unsigned* counters, unsigned* status,
+                 unsigned M, unsigned N, unsigned K, unsigned ldx, unsigned ldy, unsigned flags, unsigned TN,
+                 unsigned stages) {
+  tc::gemm_body<true>(x, w, y, bias, residual, scale_a, scale_w, partial, counters, status, M, N, K, ldx, ldy, flags,
+                      TN, stages);
+}

@@ -5,3 +5,4 @@
 #include "rope.cuh"
 #include "attention.cuh"
 #include "gemm_simt.cuh"
+#include "gemm_tc.cuh"

@@ -74,6 +74,29 @@ def ceil_div(a: int, b: int) -> int:
     return -(-a // b)
 
 
+TC_SCRATCH_BYTES = 16 << 20    # fp32 partial sums of split-K tensor-core GEMMs (zero between launches)
+TC_COUNTER_BYTES = 16 << 10    # per-tile arrival counters of the same
+TC_SMEM_BUDGET = 200 * 1024    # dynamic shared memory a tensor-core GEMM CTA may use
+
+
+def tc_tiling(M: int, N: int, K: int, elem: int, splits: int | None = None) -> dict[str, int]:
+    """Launch geometry of ``agi_gemm_tc_*``: token tile TN (multiple of 16, <= 256), K slices, ring depth."""
+    m_tiles = ceil_div(M, 256)
+    TN = ceil_div(ceil_div(M, m_tiles), 16) * 16
+    n_tiles = ceil_div(N, 128)
+    tiles = n_tiles * m_tiles
+    k_blocks = K * elem // 128
+    if splits is None:
+        # fill the 148 SMs when the output has too few tiles; keep at least two K blocks per slice
+        splits = 1 if tiles >= 120 else max(1, min(16, ceil_div(SM_COUNT, tiles), k_blocks // 2))
+    per = ceil_div(k_blocks, max(1, min(splits, k_blocks)))
+    splits = ceil_div(k_blocks, per)
+    stage_bytes = 16384 + TN * 128
+    stages = max(3, min(12, TC_SMEM_BUDGET // stage_bytes, max(per, 3)))
+    return {"TN": TN, "m_tiles": m_tiles, "n_tiles": n_tiles, "tiles": tiles, "splits": splits, "stages": stages,
+            "shared_bytes": stages * stage_bytes + 1024}
+
+
 def grid_for(work_items: int, threads: int = 256, cap: int = SM_COUNT * 8) -> int:
     return max(1, min(cap, ceil_div(work_items, threads)))
 
@@ -100,6 +123,7 @@ class RecipeBuilder:
         self.profiles: list[Profile] = []
         self.tactics: dict[tuple[str, str], dict[str, Any]] = {}
         self._profile: Profile | None = None
+        self._tc_scratch: tuple[Arena, Arena] | None = None
 
     # ---- address spaces -------------------------------------------------------------------
     def alloc(self, nbytes: int, align: int = ALIGN) -> Arena:
@@ -163,6 +187,10 @@ class RecipeBuilder:
         entry["uses"] += 1
 
     # ---- kernel families ------------------------------------------------------------------
+    def export_status(self, out: Pointer) -> None:
+        """Copy the status word (0 = every bounded wait succeeded) into a caller-visible I32 tensor."""
+        self.launch("agi_copy_u32", (1, 1, 1), (32, 1, 1), [Arena(STATUS_WORD), out, U32(1)], op="export_status")
+
     def vector_add(self, left: Pointer, right: Pointer, out: Pointer, count: int) -> None:
         self.launch("vector_add_f32", (ceil_div(count, 256), 1, 1), (256, 1, 1), [left, right, out, U32(count)],
                     op="vector_add")
@@ -227,7 +255,8 @@ class RecipeBuilder:
     def gemm(self, x: Pointer, w: Pointer, y: Pointer, M: int, N: int, K: int, *, dtype: str = "bf16",
              bias: Pointer | None = None, residual: Pointer | None = None, act: str | None = None,
              scale_a: Pointer | None = None, scale_w: Pointer | None = None, ldx: int | None = None,
-             ldy: int | None = None, out_f32: bool = False, tactic: str = "simt") -> None:
+             ldy: int | None = None, out_f32: bool = False, tactic: str = "auto",
+             splits: int | None = None) -> None:
         """Y[M, N] = epilogue(X[M, K] . W[N, K]^T); ``dtype`` names the operand type (bf16 or e4m3)."""
         flags = ACT[act] | (FLAG_BIAS if bias else 0) | (FLAG_RESIDUAL if residual else 0) | \
             (FLAG_OUT_F32 if out_f32 else 0) | (FLAG_SCALED if scale_a else 0)
@@ -235,11 +264,29 @@ class RecipeBuilder:
         dummy = Arena(0)
         args = [x, w, y, bias or dummy, residual or dummy, scale_a or dummy, scale_w or dummy, U32(M), U32(N), U32(K),
                 U32(ldx or K), U32(ldy or N), U32(flags)]
+        elem = 1 if dtype == "e4m3" else 2
+        if tactic == "auto":
+            # the tensor-core kernel needs 16-byte aligned rows and whole 128-byte K blocks
+            tactic = "tcgen05" if (K * elem) % 128 == 0 and ((ldx or K) * elem) % 16 == 0 else "simt"
         if tactic == "simt":
             self.launch(f"agi_gemm_simt_{dtype}", (ceil_div(N, 64), ceil_div(M, 64), 1), (256, 1, 1), args,
                         op=f"gemm_{dtype}", algorithm="simt_64x64x16")
             return
-        raise ValueError(f"unknown GEMM tactic {tactic!r}")
+        if tactic != "tcgen05":
+            raise ValueError(f"unknown GEMM tactic {tactic!r}")
+        if (K * elem) % 128 or ((ldx or K) * elem) % 16:
+            raise ValueError("tcgen05 GEMM needs K bytes % 128 == 0 and 16-byte aligned rows")
+        t = tc_tiling(M, N, K, elem, splits)
+        if t["splits"] > 1 and M * N * 4 > TC_SCRATCH_BYTES:
+            t = tc_tiling(M, N, K, elem, 1)
+        if self._tc_scratch is None:
+            self._tc_scratch = (self.alloc(TC_SCRATCH_BYTES), self.alloc(TC_COUNTER_BYTES))
+        partial, counters = self._tc_scratch
+        assert t["tiles"] * 4 <= TC_COUNTER_BYTES
+        self.launch(f"agi_gemm_tc_{dtype}", (t["n_tiles"], t["m_tiles"], t["splits"]), (160, 1, 1),
+                    args[:7] + [partial, counters, Arena(STATUS_WORD)] + args[7:] + [U32(t["TN"]), U32(t["stages"])],
+                    shared_bytes=t["shared_bytes"], op=f"gemm_{dtype}",
+                    algorithm=f"tcgen05_128x{t['TN']}_s{t['stages']}_k{t['splits']}")
 
     # ---- outputs --------------------------------------------------------------------------
     def plan(self) -> dict[str, Any]:

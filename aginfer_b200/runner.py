@@ -30,6 +30,7 @@ class Runner:
         self.outputs = self.session.output_info()
         self._packed = None
         self._packed_key = None
+        self._side = None
 
     def empty_outputs(self, device="cuda") -> dict:
         import torch
@@ -48,7 +49,16 @@ class Runner:
             self._packed_key = key
             self._keep = (dict(inputs), outputs)
         s = stream if stream is not None else torch.cuda.current_stream()
-        self.session.enqueue_packed(self._packed, s.cuda_stream)
+        if s.cuda_stream == 0:
+            # The legacy default stream cannot be captured, so graph replay needs a real stream:
+            # run on a side stream, ordered after and before the work on the default stream.
+            if self._side is None:
+                self._side = torch.cuda.Stream()
+            self._side.wait_stream(s)
+            self.session.enqueue_packed(self._packed, self._side.cuda_stream)
+            s.wait_stream(self._side)
+        else:
+            self.session.enqueue_packed(self._packed, s.cuda_stream)
         return outputs
 
     def stats(self) -> dict:

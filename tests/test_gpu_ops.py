@@ -179,3 +179,60 @@ def test_gemm_simt_e4m3_scaled(tmp_path):
     assert ops.max_rel_err(got["y"], want) < 1e-2
     # and the quantised product stays close to the unquantised one
     assert ops.max_rel_err(got["y"], ops.gemm(x, wf.to(BF))) < 0.1
+
+
+TC_CASES = [
+    # M, N, K, dtype, splits (None = builder's choice), epilogue
+    (17, 1536, 1536, "bf16", None, "plain"),       # DiT projection, split-K 12
+    (17, 1536, 1536, "bf16", 1, "bias_gelu_res"),  # same, one slice, full epilogue
+    (17, 6144, 1536, "bf16", None, "bias_gelu"),   # DiT MLP up
+    (17, 1536, 6144, "bf16", None, "bias_res"),    # DiT MLP down
+    (288, 2560, 2048, "bf16", None, "bias"),       # decoder QKV, two token tiles of 144
+    (288, 2048, 11008, "bf16", None, "res"),       # decoder down projection
+    (50, 1024, 4096, "bf16", None, "plain"),       # action expert
+    (1, 2048, 2048, "e4m3", None, "plain"),        # FP8 sweep corners
+    (16, 11008, 2048, "e4m3", None, "plain"),
+    (64, 2048, 11008, "e4m3", None, "plain"),
+    (288, 2560, 2048, "e4m3", None, "bias"),
+    (1024, 1536, 1536, "e4m3", None, "plain"),
+    (300, 1000, 512, "bf16", None, "bias"),        # ragged: N and M not multiples of the tile
+    (5, 130, 128, "e4m3", 1, "plain"),
+]
+
+
+@pytest.mark.parametrize("case", TC_CASES, ids=lambda c: "-".join(map(str, c)))
+def test_gemm_tcgen05(tmp_path, case):
+    M, N, K, dtype, splits, epi = case
+    x, wf = randn(M, K, seed=21), randn(N, K, seed=22, std=0.02)
+    bias = randn(N, seed=23, std=0.1) if "bias" in epi else None
+    res = randn(M, N, seed=24) if "res" in epi else None
+    act = "gelu_tanh" if "gelu" in epi else None
+    weights, inputs = {}, {"x": x}
+    if dtype == "e4m3":
+        wq, ws = ops.quantize_e4m3(wf)
+        xq, xs = ops.quantize_e4m3(x)
+        weights.update({"w": wq, "w_scale": ws.reshape(())})
+        want = ops.gemm(xq, wq, bias=bias, residual=res, act=act, scale_a=xs, scale_w=ws)
+    else:
+        weights["w"] = wf.to(BF)
+        want = ops.gemm(x, wf.to(BF), bias=bias, residual=res, act=act)
+    if bias is not None:
+        weights["b"] = bias
+    if res is not None:
+        inputs["res"] = res
+
+    def body(r):
+        kw = dict(bias=Weight("b") if bias is not None else None, residual=Tensor("res") if res is not None else None,
+                  act=act, tactic="tcgen05", splits=splits)
+        if dtype == "e4m3":
+            q, s = r.alloc(M * K), r.alloc(4)
+            r.quantize_e4m3(Tensor("x"), q, s, M * K)
+            r.gemm(q, Weight("w"), Tensor("y"), M, N, K, dtype="e4m3", scale_a=s, scale_w=Weight("w_scale"), **kw)
+        else:
+            r.gemm(Tensor("x"), Weight("w"), Tensor("y"), M, N, K, **kw)
+        r.export_status(Tensor("status"))
+
+    got, _ = run_recipe(tmp_path, weights, inputs, {"y": (BF, (M, N)), "status": (torch.int32, (1,))}, body, repeats=3)
+    assert got["status"].item() == 0, hex(got["status"].item())
+    err = ops.max_rel_err(got["y"], want)
+    assert err < (1e-2 if dtype == "bf16" else 1e-2), err
