@@ -18,9 +18,10 @@ typedef __nv_bfloat162 bf162;
 enum : unsigned {
   kFlagBias = 1u << 0,       // add bias[n]
   kFlagResidual = 1u << 1,   // add residual[m, n] (bf16, same leading dimension as the output)
-  kFlagActMask = 0xFu << 4,  // activation applied after bias: 0 none, 1 GELU(tanh), 2 SiLU
+  kFlagActMask = 0xFu << 4,  // activation applied after bias: 0 none, 1 GELU(tanh), 2 SiLU, 3 ReLU
   kActGeluTanh = 1u << 4,
   kActSilu = 2u << 4,
+  kActRelu = 3u << 4,
   kFlagOutF32 = 1u << 8,     // write fp32 instead of bf16
   kFlagScaled = 1u << 9,     // multiply the accumulator by *scale_a * *scale_w (FP8 path)
 };
@@ -79,6 +80,7 @@ __device__ __forceinline__ float apply_activation(float x, unsigned flags) {
   const unsigned act = flags & kFlagActMask;
   if (act == kActGeluTanh) return gelu_tanh(x);
   if (act == kActSilu) return silu(x);
+  if (act == kActRelu) return fmaxf(x, 0.f);
   return x;
 }
 

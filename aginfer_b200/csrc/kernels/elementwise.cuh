@@ -143,3 +143,27 @@ extern "C" __global__ void agi_add_rows_bf16(bf16* out, const bf16* addend, unsi
     out[size_t(r) * out_stride + c] = __float2bfloat16_rn(sum);
   }
 }
+
+// Sinusoidal embedding of a scalar time: out[r, :] = [cos(t_r * f_i) | sin(t_r * f_i)], i < dim / 2,
+// f_i = exp(-ln(10000) * i / (dim / 2)), t_r = t0 + r * dt.  Used for the flow-matching timestep
+// (rows = denoising steps) and for the action encoder (rows = action tokens, dt = 0).
+extern "C" __global__ void agi_timestep_embedding(bf16* out, unsigned rows, unsigned dim, unsigned out_stride,
+                                                   float t0, float dt) {
+  grid_dependency_wait();
+  const unsigned half = dim / 2;
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < rows * half; i += gridDim.x * blockDim.x) {
+    const unsigned r = i / half, k = i % half;
+    const float freq = expf(-9.210340371976184f * float(k) / float(half));
+    float s, c;
+    sincosf((t0 + float(r) * dt) * freq, &s, &c);
+    out[size_t(r) * out_stride + k] = __float2bfloat16_rn(c);
+    out[size_t(r) * out_stride + half + k] = __float2bfloat16_rn(s);
+  }
+}
+
+// Elementwise SiLU on bf16 (conditioning vector before the AdaLN projections).
+extern "C" __global__ void agi_silu_bf16(const bf16* in, bf16* out, unsigned count) {
+  grid_dependency_wait();
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < count; i += gridDim.x * blockDim.x)
+    out[i] = __float2bfloat16_rn(silu(__bfloat162float(in[i])));
+}

@@ -15,10 +15,10 @@
 // tcgen05.commit.  After the main loop the producer warps become the epilogue: each reads
 // its 32 TMEM lanes with tcgen05.ld and writes bf16 (or fp32) rows.
 //
-// Split-K.  grid.z > 1 slices K.  Each slice adds its partial tile into an fp32 scratch
-// matrix with red.global.add; a per-tile arrival counter elects the last slice, which
-// applies the epilogue, writes Y and leaves scratch and counter zeroed for the next launch.
-// Nobody spins on another CTA.
+// Split-K.  grid.z > 1 slices K.  Each slice stores its partial tile into its own fp32 slab
+// of a scratch buffer laid out [slice][M][N]; a per-tile arrival counter elects the last slice
+// to arrive, which adds the slabs in slice order (so the result does not depend on arrival
+// order), applies the epilogue, writes Y and resets the counter.  Nobody spins on another CTA.
 //
 // Every wait on an mbarrier is bounded; on expiry the kernel records a code in `status`
 // and carries on with whatever data it has, so a logic error shows up as a status word and
@@ -255,7 +255,7 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
           const unsigned m = m0 + c0 + i;
           if (m >= M) continue;
           if (splits == 1) gemm_store(v[i], m, n, y, ldy, bias, residual, alpha, flags);
-          else atomicAdd(partial + size_t(m) * N + n, v[i]);
+          else __stcg(partial + (size_t(split) * M + m) * N + n, v[i]);
         }
       }
     }
@@ -285,9 +285,8 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
       for (unsigned i = 0; i < TN; ++i) {
         const unsigned m = m0 + i;
         if (m >= M) break;
-        float* cell = partial + size_t(m) * N + n;
-        const float total = __ldcg(cell);
-        *cell = 0.f;  // scratch is handed back zeroed
+        float total = 0.f;
+        for (unsigned z = 0; z < splits; ++z) total += __ldcg(partial + (size_t(z) * M + m) * N + n);
         gemm_store(total, m, n, y, ldy, bias, residual, alpha, flags);
       }
     }

@@ -250,18 +250,32 @@ Status Session::Prepare() {
   if (workspace_ == 0 && workspace_bytes != 0)
     AGI_RETURN_IF_ERROR(cu_->Check(cu_->cuMemAlloc(&workspace_, static_cast<std::size_t>(workspace_bytes)), "cuMemAlloc", kOutOfMemory));
 
+  // Resolve each distinct kernel once; a function's dynamic shared-memory limit is a property of the
+  // function, so it is raised to the largest request any launch of the profile makes.
   functions_.clear();
   functions_.reserve(profile_->launch_count);
+  std::vector<std::pair<std::uint32_t, CUfunction>> resolved;      // name offset -> function
+  std::vector<std::uint32_t> shared_need;
   for (std::uint32_t l = 0; l < profile_->launch_count; ++l) {
     const wire::Launch& launch = plan_.launches[profile_->first_launch + l];
-    const std::string name(plan_.Text(launch.kernel));
-    CUfunction fn = nullptr;
-    AGI_RETURN_IF_ERROR(cu_->Check(cu_->cuModuleGetFunction(&fn, module_, name.c_str()), "cuModuleGetFunction(" + name + ")"));
-    if (launch.shared_bytes > kStaticSharedLimit)
-      AGI_RETURN_IF_ERROR(cu_->Check(
-          cu_->cuFuncSetAttribute(fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, static_cast<int>(launch.shared_bytes)),
-          "cuFuncSetAttribute(" + name + ")"));
-    functions_.push_back(fn);
+    std::size_t slot = 0;
+    while (slot < resolved.size() && resolved[slot].first != launch.kernel) ++slot;
+    if (slot == resolved.size()) {
+      const std::string name(plan_.Text(launch.kernel));
+      CUfunction fn = nullptr;
+      AGI_RETURN_IF_ERROR(cu_->Check(cu_->cuModuleGetFunction(&fn, module_, name.c_str()), "cuModuleGetFunction(" + name + ")"));
+      resolved.emplace_back(launch.kernel, fn);
+      shared_need.push_back(0);
+    }
+    shared_need[slot] = std::max(shared_need[slot], launch.shared_bytes);
+    functions_.push_back(resolved[slot].second);
+  }
+  for (std::size_t slot = 0; slot < resolved.size(); ++slot) {
+    if (shared_need[slot] <= kStaticSharedLimit) continue;
+    const std::string name(plan_.Text(resolved[slot].first));
+    AGI_RETURN_IF_ERROR(cu_->Check(cu_->cuFuncSetAttribute(resolved[slot].second, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES,
+                                                           static_cast<int>(shared_need[slot])),
+                                   "cuFuncSetAttribute(" + name + ")"));
   }
   prepared_ = true;
   return {};

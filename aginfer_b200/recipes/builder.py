@@ -28,7 +28,7 @@ STATUS_WORD = 0          # u32: first error recorded by a kernel (0 = none)
 SM_COUNT = 148
 
 FLAG_BIAS, FLAG_RESIDUAL, FLAG_OUT_F32, FLAG_SCALED = 1, 2, 1 << 8, 1 << 9
-ACT = {None: 0, "gelu_tanh": 1 << 4, "silu": 2 << 4}
+ACT = {None: 0, "gelu_tanh": 1 << 4, "silu": 2 << 4, "relu": 3 << 4}
 PLAN_DTYPE_BYTES = {"F32": 4, "F16": 2, "BF16": 2, "F8_E4M3": 1, "I32": 4}
 
 
@@ -74,7 +74,7 @@ def ceil_div(a: int, b: int) -> int:
     return -(-a // b)
 
 
-TC_SCRATCH_BYTES = 16 << 20    # fp32 partial sums of split-K tensor-core GEMMs (zero between launches)
+TC_SCRATCH_BYTES = 32 << 20    # fp32 partial tiles of split-K tensor-core GEMMs, [slice][M][N]
 TC_COUNTER_BYTES = 16 << 10    # per-tile arrival counters of the same
 TC_SMEM_BUDGET = 200 * 1024    # dynamic shared memory a tensor-core GEMM CTA may use
 
@@ -123,7 +123,9 @@ class RecipeBuilder:
         self.profiles: list[Profile] = []
         self.tactics: dict[tuple[str, str], dict[str, Any]] = {}
         self._profile: Profile | None = None
-        self._tc_scratch: tuple[Arena, Arena] | None = None
+        # Split-K scratch of the tensor-core GEMMs lives outside the stack discipline of alloc/release:
+        # its arrival counters must stay zero between launches for the whole life of the session.
+        self._tc_scratch = (self.alloc(TC_SCRATCH_BYTES), self.alloc(TC_COUNTER_BYTES))
 
     # ---- address spaces -------------------------------------------------------------------
     def alloc(self, nbytes: int, align: int = ALIGN) -> Arena:
@@ -277,10 +279,8 @@ class RecipeBuilder:
         if (K * elem) % 128 or ((ldx or K) * elem) % 16:
             raise ValueError("tcgen05 GEMM needs K bytes % 128 == 0 and 16-byte aligned rows")
         t = tc_tiling(M, N, K, elem, splits)
-        if t["splits"] > 1 and M * N * 4 > TC_SCRATCH_BYTES:
-            t = tc_tiling(M, N, K, elem, 1)
-        if self._tc_scratch is None:
-            self._tc_scratch = (self.alloc(TC_SCRATCH_BYTES), self.alloc(TC_COUNTER_BYTES))
+        while t["splits"] > 1 and t["splits"] * M * N * 4 > TC_SCRATCH_BYTES:
+            t = tc_tiling(M, N, K, elem, t["splits"] // 2)
         partial, counters = self._tc_scratch
         assert t["tiles"] * 4 <= TC_COUNTER_BYTES
         self.launch(f"agi_gemm_tc_{dtype}", (t["n_tiles"], t["m_tiles"], t["splits"]), (160, 1, 1),

@@ -1,0 +1,229 @@
+"""Launch recipe of a GR00T-N1.5-shaped flow-matching action head (DiT) at batch 1.
+
+Shape (``DitConfig`` defaults): 16 blocks, hidden 1536, 32 heads x 48, GELU MLP 6144, AdaLN
+conditioning on the flow time; blocks alternate cross-attention to the 300 backbone tokens
+(dim 2048; even blocks) and self-attention over 1 state token + 16 action tokens (odd
+blocks); action dim 32, state dim 64; 4 Euler steps from caller-provided noise.
+
+The whole denoising loop is ONE profile: the steps are unrolled into the launch list with
+the time of each step baked in as a scalar, so the loader replays one CUDA graph per action
+chunk.  Work that does not depend on the evolving action latent is hoisted in front of the
+loop and done once per chunk:
+  * the state token (state encoder MLP);
+  * K and V of the backbone tokens for the eight cross-attention blocks;
+  * the time embedding and every block's AdaLN (scale, shift) for all steps at once
+    (one skinny GEMM with M = steps per block instead of ``steps`` GEMVs).
+What remains per step streams each block's Q/K/V/O and MLP weights exactly once.
+
+Tensor names follow Hugging Face conventions (``<module>.weight`` / ``.bias``, weights
+``[out, in]``) so the packed blob is ordered by the reference's name sort.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Mapping
+
+from .builder import Arena, F32, RecipeBuilder, Tensor, U32, Weight, io, grid_for
+
+
+@dataclass(frozen=True)
+class DitConfig:
+    layers: int = 16
+    hidden: int = 1536
+    heads: int = 32
+    head_dim: int = 48
+    mlp: int = 6144
+    action_dim: int = 32
+    state_dim: int = 64
+    horizon: int = 16
+    backbone_tokens: int = 300
+    backbone_dim: int = 2048
+    steps: int = 4
+    encoder_hidden: int = 1024     # width of the state-encoder / action-decoder MLPs
+    out_dim: int = 1024            # DiT output width in front of the action decoder
+    time_dim: int = 256            # sinusoidal width of the flow-time embedding
+    time_buckets: int = 1000       # flow time t in [0, 1) is discretised to floor(t * buckets)
+    ln_eps: float = 1e-5
+
+    @property
+    def tokens(self) -> int:
+        return 1 + self.horizon
+
+    def is_cross(self, layer: int) -> bool:
+        return layer % 2 == 0
+
+    def step_times(self) -> list[float]:
+        """Discretised flow time fed to the embeddings at each Euler step (t = i / steps)."""
+        return [float(int(i / self.steps * self.time_buckets)) for i in range(self.steps)]
+
+
+P = "action_head"
+
+
+def weight_shapes(cfg: DitConfig) -> dict[str, tuple[int, ...]]:
+    """Every checkpoint tensor of the action head: name -> shape (all BF16)."""
+    D, s = cfg.hidden, {}
+
+    def linear(name: str, out: int, inp: int) -> None:
+        s[f"{name}.weight"] = (out, inp)
+        s[f"{name}.bias"] = (out,)
+
+    linear(f"{P}.state_encoder.fc1", cfg.encoder_hidden, cfg.state_dim)
+    linear(f"{P}.state_encoder.fc2", D, cfg.encoder_hidden)
+    linear(f"{P}.action_encoder.W1", D, cfg.action_dim)
+    linear(f"{P}.action_encoder.W2", D, 2 * D)
+    linear(f"{P}.action_encoder.W3", D, D)
+    s[f"{P}.position_embedding.weight"] = (cfg.horizon, D)
+    linear(f"{P}.dit.timestep_embedder.linear_1", D, cfg.time_dim)
+    linear(f"{P}.dit.timestep_embedder.linear_2", D, D)
+    for l in range(cfg.layers):
+        b = f"{P}.dit.blocks.{l}"
+        kv_in = cfg.backbone_dim if cfg.is_cross(l) else D
+        linear(f"{b}.norm1.linear", 2 * D, D)
+        linear(f"{b}.attn.to_q", D, D)
+        linear(f"{b}.attn.to_k", D, kv_in)
+        linear(f"{b}.attn.to_v", D, kv_in)
+        linear(f"{b}.attn.to_out", D, D)
+        linear(f"{b}.ff.fc1", cfg.mlp, D)
+        linear(f"{b}.ff.fc2", D, cfg.mlp)
+    linear(f"{P}.dit.norm_out.linear", 2 * D, D)
+    linear(f"{P}.dit.proj_out", cfg.out_dim, D)
+    linear(f"{P}.action_decoder.fc1", cfg.encoder_hidden, cfg.out_dim)
+    linear(f"{P}.action_decoder.fc2", cfg.action_dim, cfg.encoder_hidden)
+    return s
+
+
+def synthetic_weights(cfg: DitConfig, seed: int = 2, std: float = 0.02) -> dict:
+    """Random-init BF16 weights ~ N(0, std), one generator stream in name-sorted order."""
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    return {name: (torch.randn(shape, generator=g) * std).to(torch.bfloat16)
+            for name, shape in sorted(weight_shapes(cfg).items())}
+
+
+def synthetic_inputs(cfg: DitConfig, seed: int = 2) -> dict:
+    """Backbone tokens, state and initial noise ~ N(0, 1), BF16 (noise is an explicit input: the
+    loader ignores RunOptions.seed just as the reference does)."""
+    import torch
+    g = torch.Generator().manual_seed(seed + 1000)
+    return {"backbone_features": torch.randn(cfg.backbone_tokens, cfg.backbone_dim, generator=g).to(torch.bfloat16),
+            "state": torch.randn(1, cfg.state_dim, generator=g).to(torch.bfloat16),
+            "noise": torch.randn(cfg.horizon, cfg.action_dim, generator=g).to(torch.bfloat16)}
+
+
+def build_recipe(cfg: DitConfig = DitConfig(), weights: Mapping[str, tuple[str, tuple[int, ...]]] | None = None,
+                 gemm_tactic: str = "auto", profile: str = "default") -> RecipeBuilder:
+    D, T, H, S = cfg.hidden, cfg.tokens, cfg.horizon, cfg.steps
+    r = RecipeBuilder(weights or {k: ("BF16", v) for k, v in weight_shapes(cfg).items()})
+    r.begin_profile(profile, [io("backbone_features", "BF16", [cfg.backbone_tokens, cfg.backbone_dim]),
+                              io("state", "BF16", [1, cfg.state_dim]),
+                              io("noise", "BF16", [H, cfg.action_dim])],
+                    [io("actions", "F32", [H, cfg.action_dim])])
+    BF = 2
+
+    def lin(x, name, y, M, N, K, **kw):
+        r.gemm(x, Weight(f"{name}.weight"), y, M, N, K, bias=Weight(f"{name}.bias"), tactic=gemm_tactic, **kw)
+
+    def elementwise(kernel, args, count, op):
+        r.launch(kernel, (grid_for(count), 1, 1), (256, 1, 1), args, op=op)
+
+    # ---- persistent buffers ----------------------------------------------------------------
+    x_f32 = r.alloc(H * cfg.action_dim * 4)          # action latent, fp32 across the Euler steps
+    x_bf = r.alloc(H * cfg.action_dim * BF)          # its bf16 copy, input of the action encoder
+    seq = r.alloc(T * D * BF)                        # residual stream [state token; action tokens]
+    state_tok = r.alloc(D * BF)
+    mods = [r.alloc(S * 2 * D * BF) for _ in range(cfg.layers + 1)]   # AdaLN (scale | shift) per step
+    kv = {l: (r.alloc(cfg.backbone_tokens * D * BF), r.alloc(cfg.backbone_tokens * D * BF))
+          for l in range(cfg.layers) if cfg.is_cross(l)}
+
+    # ---- once per chunk --------------------------------------------------------------------
+    mark = r.mark()
+    h_state = r.alloc(cfg.encoder_hidden * BF)
+    lin(Tensor("state"), f"{P}.state_encoder.fc1", h_state, 1, cfg.encoder_hidden, cfg.state_dim, act="relu")
+    lin(h_state, f"{P}.state_encoder.fc2", state_tok, 1, D, cfg.encoder_hidden)
+    for l, (k_buf, v_buf) in kv.items():
+        b = f"{P}.dit.blocks.{l}.attn"
+        lin(Tensor("backbone_features"), f"{b}.to_k", k_buf, cfg.backbone_tokens, D, cfg.backbone_dim)
+        lin(Tensor("backbone_features"), f"{b}.to_v", v_buf, cfg.backbone_tokens, D, cfg.backbone_dim)
+    t_sin, t_hid, temb, temb_act = (r.alloc(S * cfg.time_dim * BF), r.alloc(S * D * BF), r.alloc(S * D * BF),
+                                    r.alloc(S * D * BF))
+    times = cfg.step_times()
+    dt_bucket = times[1] - times[0] if S > 1 else 0.0
+    elementwise("agi_timestep_embedding", [t_sin, U32(S), U32(cfg.time_dim), U32(cfg.time_dim), F32(times[0]),
+                                           F32(dt_bucket)], S * cfg.time_dim // 2, "timestep_embedding")
+    lin(t_sin, f"{P}.dit.timestep_embedder.linear_1", t_hid, S, D, cfg.time_dim, act="silu")
+    lin(t_hid, f"{P}.dit.timestep_embedder.linear_2", temb, S, D, D)
+    elementwise("agi_silu_bf16", [temb, temb_act, U32(S * D)], S * D, "silu")
+    for l in range(cfg.layers):
+        lin(temb_act, f"{P}.dit.blocks.{l}.norm1.linear", mods[l], S, 2 * D, D)
+    lin(temb_act, f"{P}.dit.norm_out.linear", mods[cfg.layers], S, 2 * D, D)
+    elementwise("agi_bf16_to_f32", [Tensor("noise"), x_f32, U32(H * cfg.action_dim)], H * cfg.action_dim, "cast")
+    elementwise("agi_copy_rows_bf16", [Tensor("noise"), x_bf, U32(H), U32(cfg.action_dim), U32(cfg.action_dim),
+                                       U32(cfg.action_dim)], H * cfg.action_dim, "copy")
+    r.release(mark)
+
+    # ---- per-step scratch ------------------------------------------------------------------
+    enc_cat = r.alloc(H * 2 * D * BF)     # [W1 x_t | tau(t)]
+    enc_hid = r.alloc(H * D * BF)
+    h = r.alloc(T * D * BF)               # normalised / modulated activations
+    q = r.alloc(T * D * BF)
+    k_self, v_self = r.alloc(T * D * BF), r.alloc(T * D * BF)
+    attn = r.alloc(T * D * BF)
+    ff = r.alloc(T * cfg.mlp * BF)
+    out_hid = r.alloc(T * cfg.out_dim * BF)
+    dec_hid = r.alloc(H * cfg.encoder_hidden * BF)
+    velocity = r.alloc(H * cfg.action_dim * BF)
+
+    for step in range(S):
+        mod_row = step * 2 * D * BF       # this step's (scale | shift) row inside each mods[l]
+        # action encoder: tokens 1..H of the sequence
+        lin(x_bf, f"{P}.action_encoder.W1", enc_cat, H, D, cfg.action_dim, ldy=2 * D)
+        elementwise("agi_timestep_embedding", [enc_cat + D * BF, U32(H), U32(D), U32(2 * D), F32(times[step]), F32(0.0)],
+                    H * D // 2, "timestep_embedding")
+        lin(enc_cat, f"{P}.action_encoder.W2", enc_hid, H, D, 2 * D, act="silu")
+        lin(enc_hid, f"{P}.action_encoder.W3", seq + D * BF, H, D, D)
+        elementwise("agi_add_rows_bf16", [seq + D * BF, Weight(f"{P}.position_embedding.weight"), U32(H), U32(D), U32(D),
+                                          U32(H)], H * D, "add_position_embedding")
+        elementwise("agi_copy_rows_bf16", [state_tok, seq, U32(1), U32(D), U32(D), U32(D)], D, "copy")
+
+        for l in range(cfg.layers):
+            b = f"{P}.dit.blocks.{l}"
+            scale, shift = mods[l] + mod_row, mods[l] + (mod_row + D * BF)
+            r.layernorm(seq, h, T, D, cfg.ln_eps, scale=scale, shift=shift)
+            lin(h, f"{b}.attn.to_q", q, T, D, D)
+            if cfg.is_cross(l):
+                k_buf, v_buf, kv_rows = (*kv[l], cfg.backbone_tokens)
+            else:
+                lin(h, f"{b}.attn.to_k", k_self, T, D, D)
+                lin(h, f"{b}.attn.to_v", v_self, T, D, D)
+                k_buf, v_buf, kv_rows = k_self, v_self, T
+            r.attention(q, k_buf, v_buf, attn, q_rows=T, kv_rows=kv_rows, q_heads=cfg.heads, kv_heads=cfg.heads,
+                        head_dim=cfg.head_dim, q_stride=D, k_stride=D, v_stride=D, o_stride=D)
+            lin(attn, f"{b}.attn.to_out", seq, T, D, D, residual=seq)
+            r.layernorm(seq, h, T, D, cfg.ln_eps)
+            lin(h, f"{b}.ff.fc1", ff, T, cfg.mlp, D, act="gelu_tanh")
+            lin(ff, f"{b}.ff.fc2", seq, T, D, cfg.mlp, residual=seq)
+
+        scale, shift = mods[cfg.layers] + mod_row, mods[cfg.layers] + (mod_row + D * BF)
+        r.layernorm(seq, h, T, D, cfg.ln_eps, scale=scale, shift=shift)
+        lin(h, f"{P}.dit.proj_out", out_hid, T, cfg.out_dim, D)
+        lin(out_hid + cfg.out_dim * BF, f"{P}.action_decoder.fc1", dec_hid, H, cfg.encoder_hidden, cfg.out_dim, act="relu")
+        lin(dec_hid, f"{P}.action_decoder.fc2", velocity, H, cfg.action_dim, cfg.encoder_hidden)
+        elementwise("agi_euler_step", [x_f32, velocity, x_bf, F32(1.0 / S), U32(H * cfg.action_dim)],
+                    H * cfg.action_dim, "euler_step")
+
+    r.launch("agi_copy_u32", (1, 1, 1), (256, 1, 1), [x_f32, Tensor("actions"), U32(H * cfg.action_dim)],
+             op="copy_out")
+    return r
+
+
+def algorithmic_bytes(cfg: DitConfig = DitConfig()) -> dict[str, int]:
+    """Weight bytes one action chunk must stream from HBM, by the accounting of the recipe above."""
+    shapes = weight_shapes(cfg)
+    size = {k: 2 * int(__import__("math").prod(v)) for k, v in shapes.items()}
+    once = sum(v for k, v in size.items() if any(t in k for t in (
+        "state_encoder", "timestep_embedder", "norm1.linear", "norm_out.linear")))
+    once += sum(v for k, v in size.items() if (".attn.to_k" in k or ".attn.to_v" in k)
+                and cfg.is_cross(int(k.split(".blocks.")[1].split(".")[0])))
+    per_step = sum(size.values()) - once
+    return {"once": once, "per_step": per_step, "per_chunk": once + cfg.steps * per_step, "total_weights": sum(size.values())}

@@ -41,6 +41,8 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, bias: torch.Tensor | None = None, 
         acc = gelu_tanh(acc)
     elif act == "silu":
         acc = acc * torch.sigmoid(acc)
+    elif act == "relu":
+        acc = torch.relu(acc)
     if residual is not None:
         acc = acc + residual.float()
     return acc if out_f32 else bf16_round(acc)
@@ -107,6 +109,19 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, mask: str = 
         scores = scores.masked_fill(~(j // mask_arg == i // mask_arg), float("-inf"))
     p = torch.softmax(scores, dim=-1)
     return bf16_round(torch.einsum("hij,jhd->ihd", p, vf))
+
+
+def timestep_embedding(t: torch.Tensor, dim: int) -> torch.Tensor:
+    """[cos(t f_i) | sin(t f_i)], f_i = exp(-ln(10000) i / (dim/2)); t is a 1-D tensor of times."""
+    half = dim // 2
+    freq = torch.exp(-math.log(10000.0) * torch.arange(half, dtype=torch.float32) / half)
+    arg = t.float()[:, None] * freq[None, :]
+    return bf16_round(torch.cat([arg.cos(), arg.sin()], dim=-1))
+
+
+def silu(x: torch.Tensor) -> torch.Tensor:
+    xf = x.float()
+    return bf16_round(xf * torch.sigmoid(xf))
 
 
 def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:

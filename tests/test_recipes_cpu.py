@@ -8,7 +8,7 @@ import aginfer_b200 as agi
 from aginfer_b200 import runtime as rt
 from aginfer_b200.build import build_all
 from aginfer_b200.recipes import Arena, RecipeBuilder, Tensor, U32, Weight, io
-from aginfer_b200.recipes.builder import RESERVED
+from aginfer_b200.recipes.builder import RESERVED, TC_COUNTER_BYTES, TC_SCRATCH_BYTES
 from aginfer_b200.recipes.package import build_aim, describe
 
 OVERRIDES = dict(cuda_arch_override=100, cuda_driver_version_override=12080, cuda_runtime_version_override=12080,
@@ -51,8 +51,9 @@ def test_arena_stack_discipline():
     b = r.alloc(5000)
     r.release(mark)
     c = r.alloc(100)
-    assert a.offset == RESERVED and b.offset == c.offset == RESERVED + 1024
-    assert r.arena_bytes == RESERVED + 1024 + 5120
+    base = RESERVED + TC_SCRATCH_BYTES + TC_COUNTER_BYTES   # fixed regions come first
+    assert a.offset == base and b.offset == c.offset == base + 1024
+    assert r.arena_bytes == base + 1024 + 5120
     first, second = r.counter(), r.counter(2)
     assert (first.offset, second.offset) == (64, 68)
 
