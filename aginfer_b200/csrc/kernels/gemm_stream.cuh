@@ -1,0 +1,214 @@
+// Weight-streaming skinny GEMM, bulk-copy version: Y[M, N] = epilogue(X[M, K] . W[N, K]^T), M <= 64.
+//
+// The batch-1 action head is a chain of small dependent GEMMs whose cost is the time to pull
+// each weight matrix out of HBM once.  What decides that time is how many bytes an SM has in
+// flight and how few dependent round trips a CTA makes, so this kernel moves BOTH operands with
+// bulk copies (cp.async.bulk, completing on mbarriers) and computes out of shared memory only:
+//
+//   * a CTA owns `rows` (8 or 16) output features.  K is cut into chunks of `chunk_windows`
+//     64-byte windows; one chunk of the CTA's weight rows plus the same K range of all M
+//     activation rows forms a slot (~100 KB); two slots form a ring.  For K <= one chunk (most
+//     of the action head) the CTA's entire input is requested at once.
+//   * a producer warp issues one bulk copy per row.  Weights never depend on the previous
+//     kernel, so the first slots' weight copies are issued BEFORE the grid-dependency wait: under
+//     programmatic dependent launch the next layer's weights stream while this layer finishes.
+//     Activation copies follow the wait.
+//   * four consumer warps walk the chunk in 64-byte windows (warp w takes windows w, w + 4, ...),
+//     read weight and activation fragments from shared memory (row pitch = chunk bytes + 16, which
+//     spreads the eight rows of a fragment over all banks) and issue warp-level MMAs (m16n8k16
+//     bf16 / m16n8k32 E4M3, fp32 accumulate); both operands use the 16-byte chunk's own element
+//     order along K.  Partial tiles of the four warps are added through shared memory in warp
+//     order; the epilogue applies scale, bias, activation, residual.
+//
+// Every mbarrier wait is bounded and reports through the status word instead of hanging.
+#pragma once
+
+#include "common.cuh"
+#include "gemm_simt.cuh"    // gemm_store
+#include "gemm_skinny.cuh"  // mma16n8
+
+namespace stream {
+
+constexpr int kConsumerWarps = 4;
+constexpr int kThreads = (kConsumerWarps + 1) * 32;  // + one producer warp
+constexpr int kSlots = 2;
+constexpr unsigned kSpinLimit = 1u << 22;
+constexpr unsigned kTimeoutFull = 0x400, kTimeoutEmpty = 0x500;
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void bulk_copy(unsigned dst, const void* src, unsigned bytes, unsigned bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void expect_bytes(unsigned bar, unsigned bytes) {
+  asm volatile("{ .reg .b64 t; mbarrier.arrive.expect_tx.shared::cta.b64 t, [%0], %1; }" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void arrive(unsigned bar) {
+  asm volatile("{ .reg .b64 t; mbarrier.arrive.shared::cta.b64 t, [%0]; }" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool bar_done(unsigned bar, unsigned parity) {
+  unsigned done;
+  asm volatile("{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+               : "=r"(done)
+               : "r"(bar), "r"(parity)
+               : "memory");
+  return done != 0;
+}
+__device__ __forceinline__ void bounded_wait(unsigned bar, unsigned parity, unsigned* status, unsigned code) {
+  for (unsigned spin = 0; !bar_done(bar, parity); ++spin) {
+    if (spin > kSpinLimit) {
+      atomicCAS(status, 0u, code);
+      return;
+    }
+    if (spin > 32) __nanosleep(20);
+  }
+}
+__device__ __forceinline__ uint4 lds128(unsigned addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
+template <bool kFp8, int NT>
+__device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y, const bf16* bias,
+                                     const bf16* residual, const float* scale_a, const float* scale_w,
+                                     unsigned* status, unsigned M, unsigned N, unsigned K, unsigned ldx, unsigned ldy,
+                                     unsigned flags, unsigned rows, unsigned chunk_windows) {
+  extern __shared__ __align__(128) unsigned char ring[];  // kSlots x (rows + M) x (chunk bytes + 16)
+  __shared__ __align__(8) unsigned long long full_bar[kSlots], empty_bar[kSlots];
+  constexpr int kPitch = NT * 8 + 1;
+  __shared__ float partial[kConsumerWarps][16][kPitch];
+
+  const unsigned elem = kFp8 ? 1u : 2u;
+  const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+  const unsigned row0 = blockIdx.x * rows;
+  const unsigned k_bytes = K * elem;
+  const unsigned windows = k_bytes / 64;
+  const unsigned chunks = (windows + chunk_windows - 1) / chunk_windows;
+  const unsigned pitch = chunk_windows * 64 + 16;
+  const unsigned slot_bytes = (rows + M) * pitch;
+  const unsigned ring_base = smem_u32(ring);
+
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int s = 0; s < kSlots; ++s) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&full_bar[s])));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&empty_bar[s])), "r"(kConsumerWarps));
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  if (warp == kConsumerWarps) {
+    // ---------------- producer warp ----------------
+    const size_t x_row = size_t(ldx) * elem;
+    bool waited = false;
+    for (unsigned c = 0; c < chunks; ++c) {
+      const unsigned slot = c % kSlots, round = c / kSlots;
+      const unsigned first = c * chunk_windows, count = min(chunk_windows, windows - first);
+      const unsigned bytes = count * 64;
+      const unsigned base = ring_base + slot * slot_bytes;
+      const unsigned bar = smem_u32(&full_bar[slot]);
+      if (round > 0) bounded_wait(smem_u32(&empty_bar[slot]), (round - 1) & 1, status, kTimeoutEmpty | slot);
+      if (lane == 0) expect_bytes(bar, bytes * (rows + M));
+      __syncwarp();
+      for (unsigned r = lane; r < rows; r += 32)  // rows past N re-read the last row; their results are dropped
+        bulk_copy(base + r * pitch, w + size_t(min(row0 + r, N - 1)) * k_bytes + size_t(first) * 64, bytes, bar);
+      if (!waited && (c + 1 == kSlots || c + 1 == chunks)) {
+        // The weight copies of the first slots are in flight; only now wait for the previous kernel,
+        // then fetch the activations it produced for those slots.
+        grid_dependency_wait();
+        waited = true;
+        for (unsigned cc = 0; cc <= c; ++cc) {
+          const unsigned f = cc * chunk_windows, n = min(chunk_windows, windows - f);
+          const unsigned b2 = ring_base + (cc % kSlots) * slot_bytes + rows * pitch;
+          for (unsigned m = lane; m < M; m += 32)
+            bulk_copy(b2 + m * pitch, x + m * x_row + size_t(f) * 64, n * 64, smem_u32(&full_bar[cc % kSlots]));
+        }
+      } else if (waited) {
+        for (unsigned m = lane; m < M; m += 32)
+          bulk_copy(base + (rows + m) * pitch, x + m * x_row + size_t(first) * 64, bytes, bar);
+      }
+    }
+    if (!waited) grid_dependency_wait();
+  } else {
+    // ---------------- consumer warps ----------------
+    float acc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
+    const bool two_halves = rows == 16;
+    unsigned b_off[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) b_off[nt] = (rows + min(unsigned(nt * 8) + g, M - 1)) * pitch + t * 16;
+    for (unsigned c = 0; c < chunks; ++c) {
+      const unsigned slot = c % kSlots, round = c / kSlots;
+      const unsigned count = min(chunk_windows, windows - c * chunk_windows);
+      const unsigned base = ring_base + slot * slot_bytes;
+      bounded_wait(smem_u32(&full_bar[slot]), round & 1, status, kTimeoutFull | slot);
+      const unsigned a_lo = base + g * pitch + t * 16, a_hi = a_lo + 8 * pitch;
+      for (unsigned win = warp; win < count; win += kConsumerWarps) {
+        const uint4 lo = lds128(a_lo + win * 64);
+        const uint4 hi = two_halves ? lds128(a_hi + win * 64) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const uint4 b = lds128(base + b_off[nt] + win * 64);
+          skinny::mma16n8<kFp8>(acc[nt], lo.x, hi.x, lo.y, hi.y, b.x, b.y);
+          skinny::mma16n8<kFp8>(acc[nt], lo.z, hi.z, lo.w, hi.w, b.z, b.w);
+        }
+      }
+      __syncwarp();
+      if (lane == 0 && c + kSlots < chunks) arrive(smem_u32(&empty_bar[slot]));
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      partial[warp][g][nt * 8 + 2 * t] = acc[nt][0];
+      partial[warp][g][nt * 8 + 2 * t + 1] = acc[nt][1];
+      partial[warp][g + 8][nt * 8 + 2 * t] = acc[nt][2];
+      partial[warp][g + 8][nt * 8 + 2 * t + 1] = acc[nt][3];
+    }
+  }
+  grid_dependency_release();
+  __syncthreads();
+  const float alpha = (flags & kFlagScaled) ? (*scale_a) * (*scale_w) : 1.f;
+  for (unsigned i = threadIdx.x; i < rows * M; i += kThreads) {
+    const unsigned r = i % rows, m = i / rows;
+    const unsigned n = row0 + r;
+    if (n >= N) continue;
+    float total = 0.f;
+#pragma unroll
+    for (int wq = 0; wq < kConsumerWarps; ++wq) total += partial[wq][r][m];
+    gemm_store(total, m, n, y, ldy, bias, residual, alpha, flags);
+  }
+}
+
+}  // namespace stream
+
+// grid = (ceil(N / rows), 1, 1), block = 160,
+// dynamic shared memory = min(2, chunks) * (rows + M) * (chunk_windows * 64 + 16);
+// M <= 8 * tiles; K bytes a multiple of 64; rows in {8, 16}.
+#define AGI_STREAM_KERNEL(NAME, TYPE, FP8, NT)                                                                       \
+  extern "C" __global__ void __launch_bounds__(stream::kThreads)                                                     \
+  NAME(const TYPE* x, const TYPE* w, void* y, const bf16* bias, const bf16* residual, const float* scale_a,         \
+       const float* scale_w, unsigned* status, unsigned M, unsigned N, unsigned K, unsigned ldx, unsigned ldy,      \
+       unsigned flags, unsigned rows, unsigned chunk_windows) {                                                             \
+    stream::body<FP8, NT>(reinterpret_cast<const uint8_t*>(x), reinterpret_cast<const uint8_t*>(w), y, bias,         \
+                          residual, scale_a, scale_w, status, M, N, K, ldx, ldy, flags, rows, chunk_windows);       \
+  }
+
+AGI_STREAM_KERNEL(agi_gemm_stream_bf16_t1, bf16, false, 1)
+AGI_STREAM_KERNEL(agi_gemm_stream_bf16_t2, bf16, false, 2)
+AGI_STREAM_KERNEL(agi_gemm_stream_bf16_t3, bf16, false, 3)
+AGI_STREAM_KERNEL(agi_gemm_stream_bf16_t4, bf16, false, 4)
+AGI_STREAM_KERNEL(agi_gemm_stream_bf16_t6, bf16, false, 6)
+AGI_STREAM_KERNEL(agi_gemm_stream_bf16_t8, bf16, false, 8)
+AGI_STREAM_KERNEL(agi_gemm_stream_e4m3_t1, uint8_t, true, 1)
+AGI_STREAM_KERNEL(agi_gemm_stream_e4m3_t2, uint8_t, true, 2)
+AGI_STREAM_KERNEL(agi_gemm_stream_e4m3_t3, uint8_t, true, 3)
+AGI_STREAM_KERNEL(agi_gemm_stream_e4m3_t4, uint8_t, true, 4)
+AGI_STREAM_KERNEL(agi_gemm_stream_e4m3_t6, uint8_t, true, 6)
+AGI_STREAM_KERNEL(agi_gemm_stream_e4m3_t8, uint8_t, true, 8)
+#undef AGI_STREAM_KERNEL

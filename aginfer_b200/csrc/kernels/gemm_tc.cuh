@@ -165,6 +165,7 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
   const unsigned stage_bytes = kATileBytes + TN * kRowBytes;
   const unsigned ring = (smem_u32(dynamic_smem) + 1023u) & ~1023u;  // tiles need 1024-byte alignment
   const unsigned columns = tmem_columns_for(TN);
+  const unsigned Np = gridDim.x * kTileN;  // row stride of the split-K slabs: N rounded up to whole tiles
   if (stages > kMaxStages) stages = kMaxStages;
 
   if (tid == 0) {
@@ -255,7 +256,7 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
           const unsigned m = m0 + c0 + i;
           if (m >= M) continue;
           if (splits == 1) gemm_store(v[i], m, n, y, ldy, bias, residual, alpha, flags);
-          else __stcg(partial + (size_t(split) * M + m) * N + n, v[i]);
+          else __stcg(partial + (size_t(split) * M + m) * Np + n, v[i]);
         }
       }
     }
@@ -279,16 +280,30 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
   if (!last_flag) return;
   __threadfence();
   if (warp < 4) {
-    const unsigned n = n0 + warp * 32 + lane;
+    // Warp w reduces token rows w, w + 4, ...; lane l owns output features n0 + 4l .. 4l + 3.  The
+    // loads of one row's slabs are independent, so they are all in flight together; the additions
+    // run in slice order, which makes the sum independent of which CTA arrived when.
     const float alpha = (flags & kFlagScaled) ? (*scale_a) * (*scale_w) : 1.f;
-    if (n < N) {
-      for (unsigned i = 0; i < TN; ++i) {
-        const unsigned m = m0 + i;
-        if (m >= M) break;
-        float total = 0.f;
-        for (unsigned z = 0; z < splits; ++z) total += __ldcg(partial + (size_t(z) * M + m) * N + n);
-        gemm_store(total, m, n, y, ldy, bias, residual, alpha, flags);
-      }
+    const unsigned n = n0 + lane * 4;
+    const unsigned rows = min(TN, M - m0);
+    for (unsigned i = warp; i < rows; i += 4) {
+      const unsigned m = m0 + i;
+      const float4* cell = reinterpret_cast<const float4*>(partial + size_t(m) * Np + n);
+      const size_t slab = size_t(M) * Np / 4;
+      float4 part[16];
+#pragma unroll
+      for (unsigned z = 0; z < 16; ++z)
+        if (z < splits) part[z] = __ldcg(cell + z * slab);
+      float4 total = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (unsigned z = 0; z < 16; ++z)
+        if (z < splits) {
+          total.x += part[z].x; total.y += part[z].y; total.z += part[z].z; total.w += part[z].w;
+        }
+      const float t4[4] = {total.x, total.y, total.z, total.w};
+#pragma unroll
+      for (unsigned j = 0; j < 4; ++j)
+        if (n + j < N) gemm_store(t4[j], m, n + j, y, ldy, bias, residual, alpha, flags);
     }
   }
   if (tid == 0) counters[tile] = 0;

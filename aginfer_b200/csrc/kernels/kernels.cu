@@ -6,3 +6,5 @@
 #include "attention.cuh"
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
+#include "gemm_skinny.cuh"
+#include "gemm_stream.cuh"

@@ -77,6 +77,8 @@ def ceil_div(a: int, b: int) -> int:
 TC_SCRATCH_BYTES = 32 << 20    # fp32 partial tiles of split-K tensor-core GEMMs, [slice][M][N]
 TC_COUNTER_BYTES = 16 << 10    # per-tile arrival counters of the same
 TC_SMEM_BUDGET = 200 * 1024    # dynamic shared memory a tensor-core GEMM CTA may use
+STREAM_SM_BYTES = 208 * 1024     # shared memory the bulk-stream GEMM CTAs of one SM may use together
+STREAM_CTA_BYTES = 104 * 1024    # and the most a single CTA takes (two CTAs per SM keep one draining while one fills)
 
 
 def tc_tiling(M: int, N: int, K: int, elem: int, splits: int | None = None) -> dict[str, int]:
@@ -95,6 +97,28 @@ def tc_tiling(M: int, N: int, K: int, elem: int, splits: int | None = None) -> d
     stages = max(3, min(12, TC_SMEM_BUDGET // stage_bytes, max(per, 3)))
     return {"TN": TN, "m_tiles": m_tiles, "n_tiles": n_tiles, "tiles": tiles, "splits": splits, "stages": stages,
             "shared_bytes": stages * stage_bytes + 1024}
+
+
+def stream_tiling(M: int, N: int, K: int, elem: int) -> dict[str, int]:
+    """Launch geometry of ``agi_gemm_stream_*``: rows per CTA, K windows per ring slot, slots.
+
+    Aim: at least one CTA per SM when N allows it, every CTA resident at once (one wave), and the shared
+    memory of an SM split evenly between the CTAs that share it, so that as many bytes as possible are
+    in flight.  16 rows per CTA halve the activation traffic per weight byte and are used when N is large
+    enough to still give every SM a CTA."""
+    rows = 16 if ceil_div(N, 16) >= SM_COUNT else 8
+    grid = ceil_div(N, rows)
+    per_sm = ceil_div(grid, SM_COUNT)
+    budget = min(STREAM_CTA_BYTES, STREAM_SM_BYTES // per_sm)
+    windows = K * elem // 64
+    row_bytes = lambda w: w * 64 + 16
+    if (rows + M) * row_bytes(windows) <= budget:
+        chunk_windows, slots = windows, 1
+    else:
+        chunk_windows = max(1, (budget // 2 // (rows + M) - 16) // 64)
+        slots = 2
+    return {"rows": rows, "grid": grid, "chunk_windows": chunk_windows, "slots": slots,
+            "shared_bytes": slots * (rows + M) * row_bytes(chunk_windows)}
 
 
 def grid_for(work_items: int, threads: int = 256, cap: int = SM_COUNT * 8) -> int:
@@ -267,9 +291,36 @@ class RecipeBuilder:
         args = [x, w, y, bias or dummy, residual or dummy, scale_a or dummy, scale_w or dummy, U32(M), U32(N), U32(K),
                 U32(ldx or K), U32(ldy or N), U32(flags)]
         elem = 1 if dtype == "e4m3" else 2
+        aligned = ((ldx or K) * elem) % 16 == 0
         if tactic == "auto":
-            # the tensor-core kernel needs 16-byte aligned rows and whole 128-byte K blocks
-            tactic = "tcgen05" if (K * elem) % 128 == 0 and ((ldx or K) * elem) % 16 == 0 else "simt"
+            # <= 64 tokens: weight-streaming kernel (whole 64-byte K windows); otherwise the tensor-core
+            # kernel (whole 128-byte K blocks); anything else falls back to the CUDA-core kernel.
+            if M <= 64 and (K * elem) % 64 == 0 and aligned:
+                tactic = "stream"
+            elif (K * elem) % 128 == 0 and aligned:
+                tactic = "tcgen05"
+            else:
+                tactic = "simt"
+        if tactic == "stream":
+            # both operands reach shared memory by bulk copies; K is cut into chunks of <= ~100 KB per slot
+            if M > 64 or (K * elem) % 64 or not aligned:
+                raise ValueError("stream GEMM needs M <= 64, K bytes % 64 == 0 and 16-byte aligned rows")
+            t = stream_tiling(M, N, K, elem)
+            rows, chunk_windows, slots = t["rows"], t["chunk_windows"], t["slots"]
+            tiles = next(t for t in (1, 2, 3, 4, 6, 8) if 8 * t >= M)
+            self.launch(f"agi_gemm_stream_{dtype}_t{tiles}", (ceil_div(N, rows), 1, 1), (160, 1, 1),
+                        args[:7] + [Arena(STATUS_WORD)] + args[7:] + [U32(rows), U32(chunk_windows)],
+                        shared_bytes=slots * (rows + M) * (chunk_windows * 64 + 16),
+                        op=f"gemm_{dtype}", algorithm=f"bulk_stream_r{rows}_t{tiles}_c{chunk_windows}")
+            return
+        if tactic == "skinny":
+            if M > 64 or (K * elem) % 64 or not aligned:
+                raise ValueError("skinny GEMM needs M <= 64, K bytes % 64 == 0 and 16-byte aligned rows")
+            rows = 16 if ceil_div(N, 16) >= SM_COUNT else 8
+            tiles = next(t for t in (1, 2, 3, 4, 6, 8) if 8 * t >= M)
+            self.launch(f"agi_gemm_skinny_{dtype}_t{tiles}", (ceil_div(N, rows), 1, 1), (256, 1, 1), args + [U32(rows)],
+                        op=f"gemm_{dtype}", algorithm=f"skinny_stream_r{rows}_t{tiles}")
+            return
         if tactic == "simt":
             self.launch(f"agi_gemm_simt_{dtype}", (ceil_div(N, 64), ceil_div(M, 64), 1), (256, 1, 1), args,
                         op=f"gemm_{dtype}", algorithm="simt_64x64x16")
@@ -279,7 +330,7 @@ class RecipeBuilder:
         if (K * elem) % 128 or ((ldx or K) * elem) % 16:
             raise ValueError("tcgen05 GEMM needs K bytes % 128 == 0 and 16-byte aligned rows")
         t = tc_tiling(M, N, K, elem, splits)
-        while t["splits"] > 1 and t["splits"] * M * N * 4 > TC_SCRATCH_BYTES:
+        while t["splits"] > 1 and t["splits"] * M * t["n_tiles"] * 128 * 4 > TC_SCRATCH_BYTES:
             t = tc_tiling(M, N, K, elem, t["splits"] // 2)
         partial, counters = self._tc_scratch
         assert t["tiles"] * 4 <= TC_COUNTER_BYTES

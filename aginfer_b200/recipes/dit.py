@@ -112,7 +112,7 @@ def synthetic_inputs(cfg: DitConfig, seed: int = 2) -> dict:
 
 
 def build_recipe(cfg: DitConfig = DitConfig(), weights: Mapping[str, tuple[str, tuple[int, ...]]] | None = None,
-                 gemm_tactic: str = "auto", profile: str = "default") -> RecipeBuilder:
+                 gemm_tactic: str = "auto", profile: str = "default", stream_profile: bool = False) -> RecipeBuilder:
     D, T, H, S = cfg.hidden, cfg.tokens, cfg.horizon, cfg.steps
     r = RecipeBuilder(weights or {k: ("BF16", v) for k, v in weight_shapes(cfg).items()})
     r.begin_profile(profile, [io("backbone_features", "BF16", [cfg.backbone_tokens, cfg.backbone_dim]),
@@ -214,7 +214,36 @@ def build_recipe(cfg: DitConfig = DitConfig(), weights: Mapping[str, tuple[str, 
 
     r.launch("agi_copy_u32", (1, 1, 1), (256, 1, 1), [x_f32, Tensor("actions"), U32(H * cfg.action_dim)],
              op="copy_out")
+
+    if stream_profile:
+        # Measurement profile: the tensor-core GEMM launches of ONE denoising step, back to back and
+        # nothing else (same kernels, tilings and weights as above; activations are whatever the arena
+        # holds).  Timing it gives the weight-streaming rate of the dominant kernel in isolation.
+        r.begin_profile("gemm_stream", [io("token", "I32", [1])], [io("status", "I32", [1])])
+        for l in range(cfg.layers):
+            b = f"{P}.dit.blocks.{l}"
+            lin(h, f"{b}.attn.to_q", q, T, D, D)
+            if not cfg.is_cross(l):
+                lin(h, f"{b}.attn.to_k", k_self, T, D, D)
+                lin(h, f"{b}.attn.to_v", v_self, T, D, D)
+            lin(attn, f"{b}.attn.to_out", seq, T, D, D, residual=seq)
+            lin(h, f"{b}.ff.fc1", ff, T, cfg.mlp, D, act="gelu_tanh")
+            lin(ff, f"{b}.ff.fc2", seq, T, D, cfg.mlp, residual=seq)
+        r.export_status(Tensor("status"))
     return r
+
+
+def stream_profile_bytes(cfg: DitConfig = DitConfig()) -> tuple[int, int]:
+    """(algorithmic bytes, GEMM launches) of the ``gemm_stream`` profile: per launch
+    N*K*2 (weights) + M*K*2 (activations in) + M*N*2 (out) + N*2 (bias), residual reads included."""
+    D, T, total, count = cfg.hidden, cfg.tokens, 0, 0
+    for l in range(cfg.layers):
+        shapes = [(D, D, False)] + ([] if cfg.is_cross(l) else [(D, D, False), (D, D, False)]) + \
+            [(D, D, True), (cfg.mlp, D, False), (D, cfg.mlp, True)]
+        for N, K, residual in shapes:
+            total += N * K * 2 + T * K * 2 + T * N * 2 + N * 2 + (T * N * 2 if residual else 0)
+            count += 1
+    return total, count
 
 
 def algorithmic_bytes(cfg: DitConfig = DitConfig()) -> dict[str, int]:

@@ -1,0 +1,99 @@
+"""Time one kernel family in isolation through the packaged path (AIM -> loader -> CUDA graph).
+
+    python -m aginfer_b200.recipes.kernel_bench --case gemm_fc1 --tactic stream [--pdl] [--reps 64] [--iters 20]
+
+Each profile is ``reps`` launches of one kernel back to back; GEMM cases rotate over 16 distinct weight
+matrices of the DiT action head's shapes (17 tokens, hidden 1536, MLP 6144) so that consecutive launches
+do not find their weights in L2 by accident (16 x 18.9 MB for the MLP shapes; the 4.7 MB projection
+rotates inside L2, which is noted in the output).  Prints microseconds per launch and, for GEMMs, the
+weight-streaming rate.  Used for the per-kernel numbers under ``profiles/`` and as the small, bounded
+workload for ``ncu`` captures.
+"""
+from __future__ import annotations
+
+import argparse
+import tempfile
+from pathlib import Path
+
+D, T, MLP, LAYERS = 1536, 17, 6144, 16
+GEMM_SHAPES = {"gemm_q": (D, D), "gemm_fc1": (MLP, D), "gemm_fc2": (D, MLP)}
+CASES = ("empty", "layernorm", "attn_self", "attn_cross", *GEMM_SHAPES)
+
+
+def build(case: str, tactic: str, reps: int, tokens: int, stages: int = 4):
+    import torch
+
+    from . import Arena, RecipeBuilder, Tensor, U32, Weight, io
+    from .package import describe
+
+    weights = {"bias": torch.zeros(MLP, dtype=torch.bfloat16)}
+    if case in GEMM_SHAPES:
+        n, k = GEMM_SHAPES[case]
+        g = torch.Generator().manual_seed(0)
+        for l in range(LAYERS):
+            weights[f"l{l}.w"] = (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16)
+    r = RecipeBuilder(describe(weights))
+    r.begin_profile("default", [io("token", "I32", [1])], [io("status", "I32", [1])])
+    x, y = r.alloc(64 * MLP * 2), r.alloc(64 * MLP * 2)
+    kbuf, vbuf, q = r.alloc(300 * D * 2), r.alloc(300 * D * 2), r.alloc(64 * D * 2)
+    for i in range(reps):
+        if case == "empty":
+            r.launch("agi_fill_u32", (1, 1, 1), (256, 1, 1), [Arena(64), U32(0), U32(16)])
+        elif case == "layernorm":
+            r.layernorm(x, y, tokens, D, 1e-5)
+        elif case in ("attn_self", "attn_cross"):
+            kv_rows = tokens if case == "attn_self" else 300
+            r.attention(q, kbuf, vbuf, y, q_rows=tokens, kv_rows=kv_rows, q_heads=32, kv_heads=32, head_dim=48,
+                        q_stride=D, k_stride=D, v_stride=D, o_stride=D)
+        else:
+            n, k = GEMM_SHAPES[case]
+            r.gemm(x, Weight(f"l{i % LAYERS}.w"), y, tokens, n, k, bias=Weight("bias"), tactic=tactic)
+    r.export_status(Tensor("status"))
+    return weights, r
+
+
+def main() -> None:
+    import torch
+
+    from .. import runtime as rt
+    from ..runner import Runner
+    from .package import build_aim
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", default="gemm_fc1", choices=CASES)
+    ap.add_argument("--tactic", default="auto")
+    ap.add_argument("--reps", type=int, default=64)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--tokens", type=int, default=T)
+    ap.add_argument("--pdl", action="store_true")
+    ap.add_argument("--stages", type=int, default=4, help="K partitions of the bulk-stream GEMM (1-4)")
+    args = ap.parse_args()
+
+    weights, recipe = build(args.case, args.tactic, args.reps, args.tokens, args.stages)
+    with tempfile.TemporaryDirectory() as tmp:
+        aim = build_aim(Path(tmp), weights, recipe)
+        runner = Runner(aim, flags=rt.PROGRAMMATIC_LAUNCH if args.pdl else 0)
+        token = torch.zeros(1, dtype=torch.int32, device="cuda")
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                runner.run({"token": token}, {"status": status}, stream=stream)
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            start.record(stream)
+            for _ in range(args.iters):
+                runner.run({"token": token}, {"status": status}, stream=stream)
+            end.record(stream)
+            torch.cuda.synchronize()
+        us = start.elapsed_time(end) * 1000.0 / args.iters / (args.reps + 2)
+        line = f"{args.case} tactic={args.tactic} tokens={args.tokens} pdl={args.pdl}: {us:.2f} us/launch"
+        if args.case in GEMM_SHAPES:
+            n, k = GEMM_SHAPES[args.case]
+            line += f", {n * k * 2 / us / 1e3:.0f} GB/s of weights"
+            line += " (L2-resident rotation)" if n * k * 2 * LAYERS < 126e6 else " (rotation larger than L2)"
+        print(line + f", status={status.item()}")
+
+
+if __name__ == "__main__":
+    main()

@@ -236,3 +236,51 @@ def test_gemm_tcgen05(tmp_path, case):
     assert got["status"].item() == 0, hex(got["status"].item())
     err = ops.max_rel_err(got["y"], want)
     assert err < (1e-2 if dtype == "bf16" else 1e-2), err
+
+
+SKINNY_CASES = [
+    (17, 1536, 1536, "bf16", "bias_gelu_res"), (17, 6144, 1536, "bf16", "bias_gelu"), (17, 1536, 6144, "bf16", "bias_res"),
+    (4, 3072, 1536, "bf16", "bias"), (1, 1024, 64, "bf16", "bias"), (16, 1536, 32, "bf16", "bias"),
+    (16, 32, 1024, "bf16", "bias"), (50, 1024, 4096, "bf16", "plain"), (64, 4096, 1024, "bf16", "plain"),
+    (33, 100, 96, "bf16", "bias"),
+    (1, 2048, 2048, "e4m3", "plain"), (16, 11008, 2048, "e4m3", "plain"), (64, 2048, 11008, "e4m3", "bias"),
+    (64, 2560, 2048, "e4m3", "plain"), (16, 1536, 1536, "e4m3", "plain"), (1, 6144, 1536, "e4m3", "plain"),
+]
+
+
+@pytest.mark.parametrize("tactic", ["skinny", "stream"])
+@pytest.mark.parametrize("case", SKINNY_CASES, ids=lambda c: "-".join(map(str, c)))
+def test_gemm_skinny(tmp_path, case, tactic):
+    M, N, K, dtype, epi = case
+    x, wf = randn(M, K, seed=31), randn(N, K, seed=32, std=0.02)
+    bias = randn(N, seed=33, std=0.1) if "bias" in epi else None
+    res = randn(M, N, seed=34) if "res" in epi else None
+    act = "gelu_tanh" if "gelu" in epi else None
+    weights, inputs = {}, {"x": x}
+    if dtype == "e4m3":
+        wq, ws = ops.quantize_e4m3(wf)
+        xq, xs = ops.quantize_e4m3(x)
+        weights.update({"w": wq, "w_scale": ws.reshape(())})
+        want = ops.gemm(xq, wq, bias=bias, residual=res, act=act, scale_a=xs, scale_w=ws)
+    else:
+        weights["w"] = wf.to(BF)
+        want = ops.gemm(x, wf.to(BF), bias=bias, residual=res, act=act)
+    if bias is not None:
+        weights["b"] = bias
+    if res is not None:
+        inputs["res"] = res
+
+    def body(r):
+        kw = dict(bias=Weight("b") if bias is not None else None, residual=Tensor("res") if res is not None else None,
+                  act=act, tactic=tactic)
+        if dtype == "e4m3":
+            q, s = r.alloc(M * K), r.alloc(4)
+            r.quantize_e4m3(Tensor("x"), q, s, M * K)
+            r.gemm(q, Weight("w"), Tensor("y"), M, N, K, dtype="e4m3", scale_a=s, scale_w=Weight("w_scale"), **kw)
+        else:
+            r.gemm(Tensor("x"), Weight("w"), Tensor("y"), M, N, K, **kw)
+        r.export_status(Tensor("status"))
+
+    got, _ = run_recipe(tmp_path, weights, inputs, {"y": (BF, (M, N)), "status": (torch.int32, (1,))}, body, repeats=2)
+    assert got["status"].item() == 0, hex(got["status"].item())
+    assert ops.max_rel_err(got["y"], want) < 1e-2
