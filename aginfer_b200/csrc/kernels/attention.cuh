@@ -99,3 +99,91 @@ agi_attention_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, unsigne
     if (t < dims_per_lane && d < head_dim) o[size_t(row) * o_stride + head * head_dim + d] = __float2bfloat16_rn(acc[t] * inv);
   }
 }
+
+// Same contract as agi_attention_bf16, for the case where every key a block of 8 query rows can see
+// fits in shared memory (the action head: 17 or 300 keys; a 288-token decoder layer; one vision
+// window).  All visible K and V rows of the head are fetched with one round of independent 16-byte
+// loads, then each warp handles one query row without further block-wide synchronisation:
+// scores for all keys (lane j takes keys j, j + 32, ...), one max and one sum reduction, then P.V.
+// grid = (ceil(q_rows / 8), q_heads), block = 256,
+// dynamic shared memory = span * ((head_dim + 2) + head_dim) * 2 + 8 * head_dim * 4 + 8 * span_pad * 4,
+// span = number of visible keys for a block of rows (all kv_rows for mask 0/1), span_pad = span rounded
+// up to 32.  head_dim a multiple of 8, <= 128.
+extern "C" __global__ void __launch_bounds__(kAttnWarps * 32)
+agi_attention_smem_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, unsigned q_rows, unsigned kv_rows,
+                        unsigned q_heads, unsigned kv_heads, unsigned head_dim, unsigned q_stride, unsigned k_stride,
+                        unsigned v_stride, unsigned o_stride, float scale, unsigned mask_mode, unsigned mask_arg,
+                        unsigned span_max) {
+  extern __shared__ __align__(16) unsigned char attn_smem[];
+  grid_dependency_wait();
+  const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const unsigned head = blockIdx.y, kv_head = head / (q_heads / kv_heads);
+  const unsigned first_row = blockIdx.x * kAttnWarps;
+  const unsigned last_row = min(first_row + kAttnWarps, q_rows) - 1;
+  unsigned key_begin = 0, key_end = kv_rows;
+  if (mask_mode == 1) key_end = min(kv_rows, last_row + mask_arg + 1);
+  if (mask_mode == 2) {
+    key_begin = (first_row / mask_arg) * mask_arg;
+    key_end = min(kv_rows, (last_row / mask_arg + 1) * mask_arg);
+  }
+  const unsigned span = min(key_end - key_begin, span_max);
+  const unsigned span_pad = (span_max + 31) & ~31u;
+  const unsigned k_pitch = head_dim + 2;  // elements; odd word count -> conflict-free row-per-lane reads
+  bf16* k_tile = reinterpret_cast<bf16*>(attn_smem);
+  bf16* v_tile = k_tile + size_t(span_max) * k_pitch;
+  float* q_tile = reinterpret_cast<float*>(v_tile + size_t(span_max) * head_dim);
+  float* p_tile = q_tile + kAttnWarps * head_dim;
+
+  // One pass of independent loads: 8 elements (16 bytes) of K and of V per step.
+  const unsigned vec_per_row = head_dim / 8;
+  for (unsigned i = threadIdx.x; i < span * vec_per_row; i += blockDim.x) {
+    const unsigned j = i / vec_per_row, d = (i % vec_per_row) * 8;
+    const size_t key = key_begin + j;
+    const Bf16x8 kk = *reinterpret_cast<const Bf16x8*>(k + key * k_stride + kv_head * head_dim + d);
+    const Bf16x8 vv = *reinterpret_cast<const Bf16x8*>(v + key * v_stride + kv_head * head_dim + d);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) *reinterpret_cast<bf162*>(&k_tile[j * k_pitch + d + 2 * e]) = kk.v[e];
+    *reinterpret_cast<Bf16x8*>(&v_tile[j * head_dim + d]) = vv;
+  }
+  const unsigned row = first_row + warp;
+  const bool live = row < q_rows;
+  for (unsigned d = lane; d < head_dim; d += 32)
+    q_tile[warp * head_dim + d] = live ? __bfloat162float(q[size_t(row) * q_stride + head * head_dim + d]) * scale : 0.f;
+  __syncthreads();
+  if (!live) return;
+
+  float* p = p_tile + warp * span_pad;
+  const float* qr = q_tile + warp * head_dim;
+  float best = -3.0e38f;
+  for (unsigned j = lane; j < span; j += 32) {
+    const unsigned key = key_begin + j;
+    bool visible = true;
+    if (mask_mode == 1) visible = key <= row + mask_arg;
+    if (mask_mode == 2) visible = key / mask_arg == row / mask_arg;
+    float score = 0.f;
+    const bf16* kr = k_tile + j * k_pitch;
+    for (unsigned d = 0; d < head_dim; d += 2) {
+      const float2 kk = __bfloat1622float2(*reinterpret_cast<const bf162*>(kr + d));
+      score += qr[d] * kk.x + qr[d + 1] * kk.y;
+    }
+    score = visible ? score : -3.0e38f;
+    p[j] = score;
+    best = fmaxf(best, score);
+  }
+  best = warp_max(best);
+  float sum = 0.f;
+  for (unsigned j = lane; j < span; j += 32) {
+    const float s = p[j];
+    const float e = s > -1.0e38f ? __expf(s - best) : 0.f;
+    p[j] = e;
+    sum += e;
+  }
+  sum = warp_sum(sum);
+  __syncwarp();
+  const float inv = sum > 0.f ? 1.f / sum : 0.f;
+  for (unsigned d = lane; d < head_dim; d += 32) {
+    float acc = 0.f;
+    for (unsigned j = 0; j < span; ++j) acc += p[j] * __bfloat162float(v_tile[j * head_dim + d]);
+    o[size_t(row) * o_stride + head * head_dim + d] = __float2bfloat16_rn(acc * inv);
+  }
+}

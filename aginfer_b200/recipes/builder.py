@@ -77,6 +77,7 @@ def ceil_div(a: int, b: int) -> int:
 TC_SCRATCH_BYTES = 32 << 20    # fp32 partial tiles of split-K tensor-core GEMMs, [slice][M][N]
 TC_COUNTER_BYTES = 16 << 10    # per-tile arrival counters of the same
 TC_SMEM_BUDGET = 200 * 1024    # dynamic shared memory a tensor-core GEMM CTA may use
+ATTN_SMEM_BUDGET = 160 * 1024    # dynamic shared memory of the keys-in-shared-memory attention kernel
 STREAM_SM_BYTES = 208 * 1024     # shared memory the bulk-stream GEMM CTAs of one SM may use together
 STREAM_CTA_BYTES = 104 * 1024    # and the most a single CTA takes (two CTAs per SM keep one draining while one fills)
 
@@ -263,13 +264,23 @@ class RecipeBuilder:
 
     def attention(self, q: Pointer, k: Pointer, v: Pointer, o: Pointer, *, q_rows: int, kv_rows: int, q_heads: int,
                   kv_heads: int, head_dim: int, q_stride: int, k_stride: int, v_stride: int, o_stride: int,
-                  mask: str = "none", mask_arg: int = 0, scale: float | None = None) -> None:
+                  mask: str = "none", mask_arg: int = 0, scale: float | None = None,
+                  algorithm: str = "auto") -> None:
         assert head_dim <= 128 and head_dim % 2 == 0 and q_heads % kv_heads == 0
         mode = {"none": 0, "causal": 1, "block": 2}[mask]
-        self.launch("agi_attention_bf16", (ceil_div(q_rows, 8), q_heads, 1), (256, 1, 1),
-                    [q, k, v, o, U32(q_rows), U32(kv_rows), U32(q_heads), U32(kv_heads), U32(head_dim), U32(q_stride),
-                     U32(k_stride), U32(v_stride), U32(o_stride),
-                     F32(scale if scale is not None else head_dim ** -0.5), U32(mode), U32(mask_arg)],
+        args = [q, k, v, o, U32(q_rows), U32(kv_rows), U32(q_heads), U32(kv_heads), U32(head_dim), U32(q_stride),
+                U32(k_stride), U32(v_stride), U32(o_stride), F32(scale if scale is not None else head_dim ** -0.5),
+                U32(mode), U32(mask_arg)]
+        # keys one block of 8 query rows can see: everything, or one diagonal block (plus alignment slack)
+        span = kv_rows if mask != "block" else min(kv_rows, mask_arg * (1 + ceil_div(8, mask_arg)))
+        span_pad = ceil_div(span, 32) * 32
+        smem = span * (2 * head_dim + 2) * 2 + 8 * head_dim * 4 + 8 * span_pad * 4
+        aligned = head_dim % 8 == 0 and k_stride % 8 == 0 and v_stride % 8 == 0
+        if aligned and smem <= ATTN_SMEM_BUDGET and algorithm != "warp_per_row":
+            self.launch("agi_attention_smem_bf16", (ceil_div(q_rows, 8), q_heads, 1), (256, 1, 1), args + [U32(span)],
+                        shared_bytes=smem, op=f"attention_{mask}", algorithm="keys_in_smem")
+            return
+        self.launch("agi_attention_bf16", (ceil_div(q_rows, 8), q_heads, 1), (256, 1, 1), args,
                     op=f"attention_{mask}", algorithm="warp_per_row")
 
     def swiglu(self, gate: Pointer, up: Pointer, out: Pointer, rows: int, cols: int, in_stride: int,

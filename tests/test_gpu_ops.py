@@ -133,13 +133,15 @@ ATTENTION_CASES = [
 ]
 
 
+@pytest.mark.parametrize("algorithm", ["warp_per_row", "auto"])
 @pytest.mark.parametrize("case", ATTENTION_CASES, ids=lambda c: "x".join(map(str, c)))
-def test_attention(tmp_path, case):
+def test_attention(tmp_path, case, algorithm):
     sq, skv, hq, hkv, d, mask, arg = case
     q, k, v = randn(sq, hq * d, seed=9), randn(skv, hkv * d, seed=10), randn(skv, hkv * d, seed=11)
     got, _ = run_recipe(tmp_path, {}, {"q": q, "k": k, "v": v}, {"o": (BF, (sq, hq * d))}, lambda r: r.attention(
         Tensor("q"), Tensor("k"), Tensor("v"), Tensor("o"), q_rows=sq, kv_rows=skv, q_heads=hq, kv_heads=hkv,
-        head_dim=d, q_stride=hq * d, k_stride=hkv * d, v_stride=hkv * d, o_stride=hq * d, mask=mask, mask_arg=arg))
+        head_dim=d, q_stride=hq * d, k_stride=hkv * d, v_stride=hkv * d, o_stride=hq * d, mask=mask, mask_arg=arg,
+        algorithm=algorithm))
     want = ops.attention(q.view(sq, hq, d), k.view(skv, hkv, d), v.view(skv, hkv, d), mask=mask, mask_arg=arg)
     assert ops.max_rel_err(got["o"], want.reshape(sq, -1)) < MAX_REL
 
