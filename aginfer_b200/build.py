@@ -43,12 +43,24 @@ def _run(cmd: list[str]) -> None:
 
 def build_runtime(force: bool = False) -> Path:
     sources = sorted(RUNTIME_SRC.glob("*.cc"))
-    deps = sources + sorted(RUNTIME_SRC.glob("*.h")) + [REPO / "include" / "aginfer_b200.h"]
+    device_sources = sorted(RUNTIME_SRC.glob("*.cu"))   # entry points that launch kernels through the CUDA runtime
+    deps = sources + device_sources + sorted(RUNTIME_SRC.glob("*.h")) + sorted(KERNEL_SRC.glob("*.cuh")) + \
+        [REPO / "include" / "aginfer_b200.h"]
     if force or _stale(LIBRARY, deps):
         LIB_DIR.mkdir(parents=True, exist_ok=True)
+        objects = []
+        for src in device_sources:
+            obj = LIB_DIR / (src.stem + ".o")
+            _run([nvcc(), "-c", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+                  "-Xcompiler", "-fPIC,-fvisibility=hidden", f"-I{REPO / 'include'}", f"-I{RUNTIME_SRC}",
+                  "-o", str(obj), str(src)])
+            objects.append(str(obj))
+        link = ["-ldl", "-lpthread"]
+        if objects:  # the CUDA runtime is linked statically; it finds the driver by itself at first use
+            link = [f"-L{CUDA_HOME / 'lib64'}", "-lcudart_static", "-lrt", *link]
         _run(["g++", "-std=c++20", "-O2", "-fPIC", "-shared", "-Wall", "-Wextra", "-Wpedantic", "-fvisibility=hidden",
-              f"-I{REPO / 'include'}", f"-I{CUDA_HOME / 'include'}", *map(str, sources), "-o", str(LIBRARY),
-              "-ldl", "-lpthread"])
+              f"-I{REPO / 'include'}", f"-I{CUDA_HOME / 'include'}", *map(str, sources), *objects, "-o", str(LIBRARY),
+              *link])
     return LIBRARY
 
 

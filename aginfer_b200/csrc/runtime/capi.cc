@@ -1,6 +1,7 @@
 #include "aginfer_b200.h"
 
 #include "digest.h"
+#include "error_slot.h"
 #include "session.h"
 
 #include <cstring>
@@ -75,6 +76,10 @@ agi_status FillInfo(const agi_session* session, std::uint32_t kind, std::uint32_
 }
 
 }  // namespace
+
+namespace agi {
+agi_status RecordFailure(int code, const std::string& message) { return Fail(static_cast<Code>(code), message); }
+}  // namespace agi
 
 extern "C" {
 

@@ -79,6 +79,8 @@ EXPORTS = {
     "agi_session_enqueue": (C.c_int, [C.c_void_p, C.POINTER(_TensorView), C.c_size_t, C.POINTER(_TensorView),
                                        C.c_size_t, C.c_void_p, C.c_void_p]),
     "agi_session_get_stats": (C.c_int, [C.c_void_p, C.POINTER(_Stats)]),
+    "agi_gemm_bf16_static_scratch": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32,
+                                                C.c_uint32, C.c_uint32, C.c_void_p]),
     "agi_sha256": (C.c_int, [C.c_void_p, C.c_size_t, C.c_int, C.POINTER(C.c_uint8)]),
 }
 
@@ -276,3 +278,12 @@ def sha256(data: bytes, portable: bool = False) -> bytes:
     buf = C.create_string_buffer(bytes(data), len(data))
     _check(load_library().agi_sha256(buf, len(data), int(portable), out))
     return bytes(out)
+
+
+def gemm_bf16_static_scratch(x_ptr: int, w_ptr: int, y_ptr: int, bias_ptr: int | None, M: int, N: int, K: int,
+                             splits: int = 1, stream: int = 0) -> None:
+    """``agi_gemm_bf16_static_scratch``: split-K bf16 GEMM whose scratch is a fixed array in the library,
+    for callers that must not allocate device memory.  Arguments are raw device addresses."""
+    _check(load_library().agi_gemm_bf16_static_scratch(C.c_void_p(x_ptr), C.c_void_p(w_ptr), C.c_void_p(y_ptr),
+                                                       C.c_void_p(bias_ptr) if bias_ptr else None, M, N, K, splits,
+                                                       C.c_void_p(stream)))

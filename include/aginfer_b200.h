@@ -158,6 +158,20 @@ typedef struct agi_session_stats {
 } agi_session_stats;
 AGI_API agi_status agi_session_get_stats(const agi_session* session, agi_session_stats* out);
 
+/* No counterpart in the reference.  Y[M,N] (bf16) = X[M,K] . W[N,K]^T (+ bias[N]) with the split-K
+ * tensor-core kernel of the sm100 bundle, for callers that may not allocate device memory (real-time
+ * loops with a frozen memory map, plug-in hooks and callbacks of other frameworks, processes whose
+ * memory budget is already spent): the split-K scratch is a fixed array inside the library image, so
+ * the call makes no cudaMalloc / cudaFree and no allocating library call.  All pointers are device
+ * pointers on the current device; `bias` may be NULL; K must be a multiple of 64; `splits` (1..16) is the
+ * number of K slices.  Limit: splits * M * roundup(N, 128) * 4 bytes <= 8 MiB and at most 1024 output
+ * tiles, otherwise AGI_INVALID_ARGUMENT.  The array is shared by every call on a device and keeps the
+ * last call's contents (what must be zero is cleared on `stream` first); calls that overlap on one GPU
+ * race.  The first call on each device performs one-time synchronous set-up (symbol address lookup,
+ * kernel attribute): make it during start-up, before any stream capture. */
+AGI_API agi_status agi_gemm_bf16_static_scratch(const void* x, const void* w, void* y, const void* bias, uint32_t M,
+                                                uint32_t N, uint32_t K, uint32_t splits, void* stream);
+
 /* SHA-256 of a buffer with the library's hasher (test hook; `portable` != 0 forces the
  * non-accelerated block function). Role of cpp/sha256.cc:58-103. */
 AGI_API agi_status agi_sha256(const void* data, size_t size, int portable, uint8_t out[32]);

@@ -1,0 +1,64 @@
+"""The allocation-free GEMM entry point against the packaged path.
+
+``agi_gemm_bf16_static_scratch`` exists for hosts that cannot call cudaMalloc at run time (a control loop
+with a frozen memory map, a plug-in hook inside another framework, a process whose device memory is
+already fully handed out): its split-K scratch is a fixed array in the library image.  This test calls it
+through the C ABI with plain device pointers and checks that it returns exactly what the existing entry
+point (``agi_session_enqueue`` of a one-GEMM recipe, scratch in the session arena) returns, twice in a
+row, because the second call meets the array as the first one left it.  The file sorts last so that a
+run stopping at the first failure has already run every other test.
+"""
+from __future__ import annotations
+
+import pytest
+import torch
+
+from aginfer_b200 import runtime as rt
+from aginfer_b200.recipes import Tensor, Weight
+from tests.gpu_util import run_recipe
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+def reference_through_session(tmp_path, x, w, bias, splits):
+    M, K = x.shape
+    N = w.shape[0]
+    got, _ = run_recipe(tmp_path, {"w": w, "b": bias}, {"x": x}, {"y": (BF, (M, N))}, lambda r: r.gemm(
+        Tensor("x"), Weight("w"), Tensor("y"), M, N, K, bias=Weight("b"), tactic="tcgen05", splits=splits))
+    return got["y"]
+
+
+@pytest.mark.parametrize("M,N,K,splits", [(17, 1536, 1536, 12), (288, 2560, 2048, 2), (50, 1000, 4096, 1)])
+def test_static_scratch_gemm_equals_session_gemm_twice(tmp_path, M, N, K, splits):
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(M, K, generator=g).to(BF)
+    w = (torch.randn(N, K, generator=g) * 0.02).to(BF)
+    bias = (torch.randn(N, generator=g) * 0.1).to(BF)
+    want = reference_through_session(tmp_path, x, w, bias, splits)
+
+    dx, dw, db = x.cuda(), w.cuda(), bias.cuda()
+    stream = torch.cuda.Stream()
+    for attempt in range(2):
+        dy = torch.full((M, N), float("nan"), dtype=BF, device="cuda")
+        torch.cuda.synchronize()
+        rt.gemm_bf16_static_scratch(dx.data_ptr(), dw.data_ptr(), dy.data_ptr(), db.data_ptr(), M, N, K, splits,
+                                    stream.cuda_stream)
+        stream.synchronize()
+        # same kernel, same tiling, slice-ordered summation: the two paths agree bit for bit
+        assert torch.equal(dy.cpu(), want), f"call {attempt + 1} differs from the session path"
+
+
+def test_static_scratch_gemm_refuses_what_does_not_fit():
+    x = torch.zeros(1024, 2048, dtype=BF, device="cuda")
+    w = torch.zeros(4096, 2048, dtype=BF, device="cuda")
+    y = torch.empty(1024, 4096, dtype=BF, device="cuda")
+    with pytest.raises(rt.RuntimeStatusError, match="built-in array holds") as caught:
+        rt.gemm_bf16_static_scratch(x.data_ptr(), w.data_ptr(), y.data_ptr(), None, 1024, 4096, 2048, 8)
+    assert caught.value.name == "INVALID_ARGUMENT"
+    with pytest.raises(rt.RuntimeStatusError, match="multiple of 64"):
+        rt.gemm_bf16_static_scratch(x.data_ptr(), w.data_ptr(), y.data_ptr(), None, 4, 4, 100, 1)
+    # one slice needs no scratch at all, so the same shape is accepted
+    rt.gemm_bf16_static_scratch(x.data_ptr(), w.data_ptr(), y.data_ptr(), None, 1024, 4096, 2048, 1)
+    torch.cuda.synchronize()
+    assert float(y.float().abs().max()) == 0.0
