@@ -56,6 +56,7 @@ const CudaApi* CudaApi::Get(std::string* why) {
       AGI_BIND(cuModuleGetFunction, "cuModuleGetFunction");
       AGI_BIND(cuModuleUnload, "cuModuleUnload");
       AGI_BIND(cuFuncSetAttribute, "cuFuncSetAttribute");
+      AGI_BIND(cuFuncGetAttribute, "cuFuncGetAttribute");
       AGI_BIND(cuMemAlloc, "cuMemAlloc_v2");
       AGI_BIND(cuMemFree, "cuMemFree_v2");
       AGI_BIND(cuMemHostAlloc, "cuMemHostAlloc");

@@ -39,6 +39,7 @@ struct CudaApi {
   AGI_CUDA_FN(cuModuleGetFunction);
   AGI_CUDA_FN(cuModuleUnload);
   AGI_CUDA_FN(cuFuncSetAttribute);
+  AGI_CUDA_FN(cuFuncGetAttribute);
   AGI_CUDA_FN(cuMemAlloc);
   AGI_CUDA_FN(cuMemFree);
   AGI_CUDA_FN(cuMemHostAlloc);

@@ -271,7 +271,10 @@ Status Session::Prepare() {
     functions_.push_back(resolved[slot].second);
   }
   for (std::size_t slot = 0; slot < resolved.size(); ++slot) {
-    if (shared_need[slot] <= kStaticSharedLimit) continue;
+    // Static and dynamic shared memory together may not pass 48 KB without the opt-in attribute.
+    int static_bytes = 0;
+    cu_->cuFuncGetAttribute(&static_bytes, CU_FUNC_ATTRIBUTE_SHARED_SIZE_BYTES, resolved[slot].second);
+    if (shared_need[slot] + static_cast<std::uint32_t>(static_bytes) <= kStaticSharedLimit) continue;
     const std::string name(plan_.Text(resolved[slot].first));
     AGI_RETURN_IF_ERROR(cu_->Check(cu_->cuFuncSetAttribute(resolved[slot].second, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES,
                                                            static_cast<int>(shared_need[slot])),

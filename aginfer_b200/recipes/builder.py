@@ -77,7 +77,7 @@ def ceil_div(a: int, b: int) -> int:
 TC_SCRATCH_BYTES = 32 << 20    # fp32 partial tiles of split-K tensor-core GEMMs, [slice][M][N]
 TC_COUNTER_BYTES = 16 << 10    # per-tile arrival counters of the same
 TC_SMEM_BUDGET = 200 * 1024    # dynamic shared memory a tensor-core GEMM CTA may use
-ATTN_SMEM_BUDGET = 160 * 1024    # dynamic shared memory of the keys-in-shared-memory attention kernel
+ATTN_SMEM_BUDGET = 200 * 1024    # dynamic shared memory of the keys-in-shared-memory attention kernel
 STREAM_SM_BYTES = 208 * 1024     # shared memory the bulk-stream GEMM CTAs of one SM may use together
 STREAM_CTA_BYTES = 104 * 1024    # and the most a single CTA takes (two CTAs per SM keep one draining while one fills)
 
