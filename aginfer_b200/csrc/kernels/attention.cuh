@@ -106,7 +106,7 @@ agi_attention_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, unsigne
 // loads, then each warp handles one query row without further block-wide synchronisation:
 // scores for all keys (lane j takes keys j, j + 32, ...), one max and one sum reduction, then P.V.
 // grid = (ceil(q_rows / 8), q_heads), block = 256,
-// dynamic shared memory = span * ((head_dim + 2) + head_dim) * 2 + 8 * head_dim * 4 + 8 * span_pad * 4,
+// dynamic shared memory = span * ((head_dim + 2) + head_dim) * 2 + 16 + 8 * head_dim * 4 + 8 * span_pad * 4,
 // span = number of visible keys for a block of rows (all kv_rows for mask 0/1), span_pad = span rounded
 // up to 32.  head_dim a multiple of 8, <= 128.
 extern "C" __global__ void __launch_bounds__(kAttnWarps * 32)
@@ -130,20 +130,37 @@ agi_attention_smem_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, un
   const unsigned span_pad = (span_max + 31) & ~31u;
   const unsigned k_pitch = head_dim + 2;  // elements; odd word count -> conflict-free row-per-lane reads
   bf16* k_tile = reinterpret_cast<bf16*>(attn_smem);
-  bf16* v_tile = k_tile + size_t(span_max) * k_pitch;
+  bf16* v_tile = k_tile + ((size_t(span_max) * k_pitch + 7) & ~size_t(7));  // keep V rows 16-byte aligned
   float* q_tile = reinterpret_cast<float*>(v_tile + size_t(span_max) * head_dim);
   float* p_tile = q_tile + kAttnWarps * head_dim;
 
-  // One pass of independent loads: 8 elements (16 bytes) of K and of V per step.
+  // Batches of independent 16-byte loads (8 elements of K and of V each), all issued before any is
+  // stored, so a batch costs one memory round trip.
   const unsigned vec_per_row = head_dim / 8;
-  for (unsigned i = threadIdx.x; i < span * vec_per_row; i += blockDim.x) {
-    const unsigned j = i / vec_per_row, d = (i % vec_per_row) * 8;
-    const size_t key = key_begin + j;
-    const Bf16x8 kk = *reinterpret_cast<const Bf16x8*>(k + key * k_stride + kv_head * head_dim + d);
-    const Bf16x8 vv = *reinterpret_cast<const Bf16x8*>(v + key * v_stride + kv_head * head_dim + d);
+  const unsigned vectors = span * vec_per_row;
+  constexpr int kBatch = 4;
+  for (unsigned i0 = threadIdx.x; i0 < vectors; i0 += kBatch * blockDim.x) {
+    uint4 kk[kBatch], vv[kBatch];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) *reinterpret_cast<bf162*>(&k_tile[j * k_pitch + d + 2 * e]) = kk.v[e];
-    *reinterpret_cast<Bf16x8*>(&v_tile[j * head_dim + d]) = vv;
+    for (int b = 0; b < kBatch; ++b) {
+      const unsigned i = i0 + b * blockDim.x;
+      if (i < vectors) {
+        const unsigned j = i / vec_per_row, d = (i % vec_per_row) * 8;
+        const size_t key = key_begin + j;
+        kk[b] = __ldg(reinterpret_cast<const uint4*>(k + key * k_stride + kv_head * head_dim + d));
+        vv[b] = __ldg(reinterpret_cast<const uint4*>(v + key * v_stride + kv_head * head_dim + d));
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b) {
+      const unsigned i = i0 + b * blockDim.x;
+      if (i < vectors) {
+        const unsigned j = i / vec_per_row, d = (i % vec_per_row) * 8;
+        unsigned* kd = reinterpret_cast<unsigned*>(&k_tile[j * k_pitch + d]);  // 4-byte aligned (pitch is even)
+        kd[0] = kk[b].x; kd[1] = kk[b].y; kd[2] = kk[b].z; kd[3] = kk[b].w;
+        *reinterpret_cast<uint4*>(&v_tile[j * head_dim + d]) = vv[b];
+      }
+    }
   }
   const unsigned row = first_row + warp;
   const bool live = row < q_rows;
@@ -155,35 +172,68 @@ agi_attention_smem_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, un
   float* p = p_tile + warp * span_pad;
   const float* qr = q_tile + warp * head_dim;
   float best = -3.0e38f;
-  for (unsigned j = lane; j < span; j += 32) {
-    const unsigned key = key_begin + j;
-    bool visible = true;
-    if (mask_mode == 1) visible = key <= row + mask_arg;
-    if (mask_mode == 2) visible = key / mask_arg == row / mask_arg;
-    float score = 0.f;
-    const bf16* kr = k_tile + j * k_pitch;
+  // Scores: 8 keys per lane per pass (keys lane, lane + 32, ...), the query pair read once per pass.
+  for (unsigned j0 = 0; j0 < span; j0 += 256) {
+    float score[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) score[i] = 0.f;
+    const unsigned groups = min(8u, (span - j0 + 31) / 32);  // 32-key groups that exist in this pass
     for (unsigned d = 0; d < head_dim; d += 2) {
-      const float2 kk = __bfloat1622float2(*reinterpret_cast<const bf162*>(kr + d));
-      score += qr[d] * kk.x + qr[d + 1] * kk.y;
+      const float2 qq = *reinterpret_cast<const float2*>(qr + d);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (i >= groups) break;
+        const unsigned j = min(j0 + lane + 32 * i, span - 1);  // clamped lanes recompute the last key; dropped below
+        const float2 kk = __bfloat1622float2(*reinterpret_cast<const bf162*>(k_tile + j * k_pitch + d));
+        score[i] += qq.x * kk.x + qq.y * kk.y;
+      }
     }
-    score = visible ? score : -3.0e38f;
-    p[j] = score;
-    best = fmaxf(best, score);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const unsigned j = j0 + lane + 32 * i;
+      if (j >= span) continue;
+      const unsigned key = key_begin + j;
+      bool visible = true;
+      if (mask_mode == 1) visible = key <= row + mask_arg;
+      if (mask_mode == 2) visible = key / mask_arg == row / mask_arg;
+      const float sc = visible ? score[i] : -3.0e38f;
+      p[j] = sc;
+      best = fmaxf(best, sc);
+    }
   }
   best = warp_max(best);
   float sum = 0.f;
   for (unsigned j = lane; j < span; j += 32) {
-    const float s = p[j];
-    const float e = s > -1.0e38f ? __expf(s - best) : 0.f;
+    const float sc = p[j];
+    const float e = sc > -1.0e38f ? __expf(sc - best) : 0.f;
     p[j] = e;
     sum += e;
   }
   sum = warp_sum(sum);
   __syncwarp();
   const float inv = sum > 0.f ? 1.f / sum : 0.f;
-  for (unsigned d = lane; d < head_dim; d += 32) {
-    float acc = 0.f;
-    for (unsigned j = 0; j < span; ++j) acc += p[j] * __bfloat162float(v_tile[j * head_dim + d]);
-    o[size_t(row) * o_stride + head * head_dim + d] = __float2bfloat16_rn(acc * inv);
+  // P.V: a lane owns two adjacent output dimensions; four keys per step on independent accumulators.
+  for (unsigned d = 2 * lane; d < head_dim; d += 64) {
+    float2 acc[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) acc[u] = make_float2(0.f, 0.f);
+    unsigned j = 0;
+    for (; j + 4 <= span; j += 4) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float pj = p[j + u];
+        const float2 vv = __bfloat1622float2(*reinterpret_cast<const bf162*>(v_tile + (j + u) * head_dim + d));
+        acc[u].x += pj * vv.x;
+        acc[u].y += pj * vv.y;
+      }
+    }
+    for (; j < span; ++j) {
+      const float pj = p[j];
+      const float2 vv = __bfloat1622float2(*reinterpret_cast<const bf162*>(v_tile + j * head_dim + d));
+      acc[0].x += pj * vv.x;
+      acc[0].y += pj * vv.y;
+    }
+    const float ox = (acc[0].x + acc[1].x) + (acc[2].x + acc[3].x), oy = (acc[0].y + acc[1].y) + (acc[2].y + acc[3].y);
+    *reinterpret_cast<bf162*>(o + size_t(row) * o_stride + head * head_dim + d) = __floats2bfloat162_rn(ox * inv, oy * inv);
   }
 }

@@ -24,6 +24,8 @@ enum : unsigned {
   kActRelu = 3u << 4,
   kFlagOutF32 = 1u << 8,     // write fp32 instead of bf16
   kFlagScaled = 1u << 9,     // multiply the accumulator by *scale_a * *scale_w (FP8 path)
+  kFlagLayerNorm = 1u << 10, // fused prologue: LayerNorm (no affine) over each activation row before the GEMM
+  kFlagLnModulate = 1u << 11, // ... followed by y * (1 + scale[k]) + shift[k] (AdaLN)
 };
 
 // Programmatic dependent launch: when the loader launches with programmatic stream

@@ -71,11 +71,24 @@ __device__ __forceinline__ uint4 lds128(unsigned addr) {
   return v;
 }
 
+// Optional extras of the fused bf16 family: up to three weight matrices side by side along N (e.g. Q | K | V,
+// each a multiple of `rows` wide, written to consecutive column blocks of y) and a LayerNorm prologue.
+struct Extra {
+  const uint8_t* w1 = nullptr;
+  const uint8_t* w2 = nullptr;
+  const bf16* bias1 = nullptr;
+  const bf16* bias2 = nullptr;
+  unsigned n1 = 0, n2 = 0;
+  const bf16* ln_scale = nullptr;
+  const bf16* ln_shift = nullptr;
+  float ln_eps = 0.f;
+};
+
 template <bool kFp8, int NT>
 __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y, const bf16* bias,
                                      const bf16* residual, const float* scale_a, const float* scale_w,
                                      unsigned* status, unsigned M, unsigned N, unsigned K, unsigned ldx, unsigned ldy,
-                                     unsigned flags, unsigned rows, unsigned chunk_windows) {
+                                     unsigned flags, unsigned rows, unsigned chunk_windows, const Extra extra = Extra()) {
   extern __shared__ __align__(128) unsigned char ring[];  // kSlots x (rows + M) x (chunk bytes + 16)
   __shared__ __align__(8) unsigned long long full_bar[kSlots], empty_bar[kSlots];
   constexpr int kPitch = NT * 8 + 1;
@@ -88,8 +101,19 @@ __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y
   const unsigned windows = k_bytes / 64;
   const unsigned chunks = (windows + chunk_windows - 1) / chunk_windows;
   const unsigned pitch = chunk_windows * 64 + 16;
-  const unsigned slot_bytes = (rows + M) * pitch;
+  constexpr unsigned mod_rows = 0;
+  const unsigned slot_bytes = (rows + M + mod_rows) * pitch;
   const unsigned ring_base = smem_u32(ring);
+  // Which of the side-by-side weight matrices this CTA's rows belong to.
+  unsigned seg_rows = N, local0 = row0, col0 = 0;
+  const uint8_t* w_seg = w;
+  const bf16* bias_seg = bias;
+  if (local0 >= seg_rows && extra.n1 != 0) {
+    local0 -= seg_rows; col0 += seg_rows; seg_rows = extra.n1; w_seg = extra.w1; bias_seg = extra.bias1;
+    if (local0 >= seg_rows && extra.n2 != 0) {
+      local0 -= seg_rows; col0 += seg_rows; seg_rows = extra.n2; w_seg = extra.w2; bias_seg = extra.bias2;
+    }
+  }
 
   if (threadIdx.x == 0) {
 #pragma unroll
@@ -112,10 +136,10 @@ __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y
       const unsigned base = ring_base + slot * slot_bytes;
       const unsigned bar = smem_u32(&full_bar[slot]);
       if (round > 0) bounded_wait(smem_u32(&empty_bar[slot]), (round - 1) & 1, status, kTimeoutEmpty | slot);
-      if (lane == 0) expect_bytes(bar, bytes * (rows + M));
+      if (lane == 0) expect_bytes(bar, bytes * (rows + M + mod_rows));
       __syncwarp();
       for (unsigned r = lane; r < rows; r += 32)  // rows past N re-read the last row; their results are dropped
-        bulk_copy(base + r * pitch, w + size_t(min(row0 + r, N - 1)) * k_bytes + size_t(first) * 64, bytes, bar);
+        bulk_copy(base + r * pitch, w_seg + size_t(min(local0 + r, seg_rows - 1)) * k_bytes + size_t(first) * 64, bytes, bar);
       if (!waited && (c + 1 == kSlots || c + 1 == chunks)) {
         // The weight copies of the first slots are in flight; only now wait for the previous kernel,
         // then fetch the activations it produced for those slots.
@@ -148,7 +172,70 @@ __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y
       const unsigned slot = c % kSlots, round = c / kSlots;
       const unsigned count = min(chunk_windows, windows - c * chunk_windows);
       const unsigned base = ring_base + slot * slot_bytes;
+      // AdaLN vectors (one value per column, up to 6 x 8 columns per lane: K <= 1536) are fetched from global
+      // memory while the slot is still filling.
+      Bf16x8 mod_scale[6], mod_shift[6];
+      if (!kFp8 && (flags & kFlagLnModulate) && c == 0) {
+#pragma unroll
+        for (int i = 0; i < 6; ++i) {
+          const unsigned v = lane + 32 * i;
+          if (v < K / 8) {
+            mod_scale[i] = *reinterpret_cast<const Bf16x8*>(extra.ln_scale + 8 * v);
+            mod_shift[i] = *reinterpret_cast<const Bf16x8*>(extra.ln_shift + 8 * v);
+          }
+        }
+      }
       bounded_wait(smem_u32(&full_bar[slot]), round & 1, status, kTimeoutFull | slot);
+      if (!kFp8 && (flags & kFlagLayerNorm) && c == 0) {
+        // Fused LayerNorm (whole rows are in this slot: the recipe only sets the flag when K is one chunk).
+        // Warp w normalises rows w, w + 4, ... in place, rounding to bf16 exactly where the stand-alone
+        // kernel would have stored them; then the four consumer warps meet before anyone multiplies.
+        unsigned char* slot_ptr = ring + slot * slot_bytes;
+        const unsigned vecs = K / 8;
+        for (unsigned m = warp; m < M; m += kConsumerWarps) {
+          Bf16x8* xr = reinterpret_cast<Bf16x8*>(slot_ptr + (rows + m) * pitch);
+          float sum = 0.f;
+          for (unsigned i = lane; i < vecs; i += 32) {
+            float f[8];
+            unpack8(xr[i], f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sum += f[j];
+          }
+          const float mean = warp_sum(sum) / float(K);
+          float var = 0.f;
+          for (unsigned i = lane; i < vecs; i += 32) {
+            float f[8];
+            unpack8(xr[i], f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) var += (f[j] - mean) * (f[j] - mean);
+          }
+          const float rstd = rsqrtf(warp_sum(var) / float(K) + extra.ln_eps);
+          if (flags & kFlagLnModulate) {
+#pragma unroll
+            for (int q = 0; q < 6; ++q) {
+              const unsigned i = lane + 32 * q;
+              if (i < vecs) {
+                float f[8], a[8], b[8];
+                unpack8(xr[i], f);
+                unpack8(mod_scale[q], a);
+                unpack8(mod_shift[q], b);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = (f[j] - mean) * rstd * (1.f + a[j]) + b[j];
+                xr[i] = pack8(f);
+              }
+            }
+          } else {
+            for (unsigned i = lane; i < vecs; i += 32) {
+              float f[8];
+              unpack8(xr[i], f);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) f[j] = (f[j] - mean) * rstd;
+              xr[i] = pack8(f);
+            }
+          }
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
+      }
       const unsigned a_lo = base + g * pitch + t * 16, a_hi = a_lo + 8 * pitch;
       for (unsigned win = warp; win < count; win += kConsumerWarps) {
         const uint4 lo = lds128(a_lo + win * 64);
@@ -176,12 +263,13 @@ __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y
   const float alpha = (flags & kFlagScaled) ? (*scale_a) * (*scale_w) : 1.f;
   for (unsigned i = threadIdx.x; i < rows * M; i += kThreads) {
     const unsigned r = i % rows, m = i / rows;
-    const unsigned n = row0 + r;
-    if (n >= N) continue;
+    if (local0 + r >= seg_rows) continue;
     float total = 0.f;
 #pragma unroll
     for (int wq = 0; wq < kConsumerWarps; ++wq) total += partial[wq][r][m];
-    gemm_store(total, m, n, y, ldy, bias, residual, alpha, flags);
+    // bias is indexed inside its own matrix, the output column across all of them
+    const unsigned n = col0 + local0 + r;
+    gemm_store(total, m, n, y, ldy, bias_seg - col0, residual, alpha, flags);
   }
 }
 
@@ -198,6 +286,38 @@ __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y
     stream::body<FP8, NT>(reinterpret_cast<const uint8_t*>(x), reinterpret_cast<const uint8_t*>(w), y, bias,         \
                           residual, scale_a, scale_w, status, M, N, K, ldx, ldy, flags, rows, chunk_windows);       \
   }
+
+// The fused bf16 family: up to three weight matrices side by side along N (N0 | N1 | N2, zeros when unused)
+// and an optional LayerNorm / AdaLN prologue over the activation rows (flags kFlagLayerNorm, kFlagLnModulate;
+// needs K in one chunk, and K <= 1536 when modulating).
+#define AGI_STREAM_FUSED_KERNEL(NAME, NT)                                                                            \
+  extern "C" __global__ void __launch_bounds__(stream::kThreads)                                                     \
+  NAME(const bf16* x, const bf16* w0, const bf16* w1, const bf16* w2, void* y, const bf16* bias0, const bf16* bias1, \
+       const bf16* bias2, const bf16* residual, const bf16* ln_scale, const bf16* ln_shift, unsigned* status,        \
+       unsigned M, unsigned N0, unsigned N1, unsigned N2, unsigned K, unsigned ldx, unsigned ldy, unsigned flags,    \
+       unsigned rows, unsigned chunk_windows, float ln_eps) {                                                        \
+    stream::Extra extra;                                                                                             \
+    extra.w1 = reinterpret_cast<const uint8_t*>(w1);                                                                 \
+    extra.w2 = reinterpret_cast<const uint8_t*>(w2);                                                                 \
+    extra.bias1 = bias1;                                                                                             \
+    extra.bias2 = bias2;                                                                                             \
+    extra.n1 = N1;                                                                                                   \
+    extra.n2 = N2;                                                                                                   \
+    extra.ln_scale = ln_scale;                                                                                       \
+    extra.ln_shift = ln_shift;                                                                                       \
+    extra.ln_eps = ln_eps;                                                                                           \
+    stream::body<false, NT>(reinterpret_cast<const uint8_t*>(x), reinterpret_cast<const uint8_t*>(w0), y, bias0,     \
+                            residual, nullptr, nullptr, status, M, N0, K, ldx, ldy, flags, rows, chunk_windows,     \
+                            extra);                                                                                  \
+  }
+
+AGI_STREAM_FUSED_KERNEL(agi_gemm_stream_fused_bf16_t1, 1)
+AGI_STREAM_FUSED_KERNEL(agi_gemm_stream_fused_bf16_t2, 2)
+AGI_STREAM_FUSED_KERNEL(agi_gemm_stream_fused_bf16_t3, 3)
+AGI_STREAM_FUSED_KERNEL(agi_gemm_stream_fused_bf16_t4, 4)
+AGI_STREAM_FUSED_KERNEL(agi_gemm_stream_fused_bf16_t6, 6)
+AGI_STREAM_FUSED_KERNEL(agi_gemm_stream_fused_bf16_t8, 8)
+#undef AGI_STREAM_FUSED_KERNEL
 
 AGI_STREAM_KERNEL(agi_gemm_stream_bf16_t1, bf16, false, 1)
 AGI_STREAM_KERNEL(agi_gemm_stream_bf16_t2, bf16, false, 2)

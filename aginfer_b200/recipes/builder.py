@@ -28,6 +28,7 @@ STATUS_WORD = 0          # u32: first error recorded by a kernel (0 = none)
 SM_COUNT = 148
 
 FLAG_BIAS, FLAG_RESIDUAL, FLAG_OUT_F32, FLAG_SCALED = 1, 2, 1 << 8, 1 << 9
+FLAG_LAYERNORM, FLAG_LN_MODULATE = 1 << 10, 1 << 11
 ACT = {None: 0, "gelu_tanh": 1 << 4, "silu": 2 << 4, "relu": 3 << 4}
 PLAN_DTYPE_BYTES = {"F32": 4, "F16": 2, "BF16": 2, "F8_E4M3": 1, "I32": 4}
 
@@ -100,7 +101,7 @@ def tc_tiling(M: int, N: int, K: int, elem: int, splits: int | None = None) -> d
             "shared_bytes": stages * stage_bytes + 1024}
 
 
-def stream_tiling(M: int, N: int, K: int, elem: int) -> dict[str, int]:
+def stream_tiling(M: int, N: int, K: int, elem: int, extra_rows: int = 0) -> dict[str, int]:
     """Launch geometry of ``agi_gemm_stream_*``: rows per CTA, K windows per ring slot, slots.
 
     Aim: at least one CTA per SM when N allows it, every CTA resident at once (one wave), and the shared
@@ -113,13 +114,14 @@ def stream_tiling(M: int, N: int, K: int, elem: int) -> dict[str, int]:
     budget = min(STREAM_CTA_BYTES, STREAM_SM_BYTES // per_sm)
     windows = K * elem // 64
     row_bytes = lambda w: w * 64 + 16
-    if (rows + M) * row_bytes(windows) <= budget:
+    held = rows + M + extra_rows   # rows of a ring slot: weights, activations, optional AdaLN vectors
+    if held * row_bytes(windows) <= budget:
         chunk_windows, slots = windows, 1
     else:
-        chunk_windows = max(1, (budget // 2 // (rows + M) - 16) // 64)
+        chunk_windows = max(1, (budget // 2 // held - 16) // 64)
         slots = 2
     return {"rows": rows, "grid": grid, "chunk_windows": chunk_windows, "slots": slots,
-            "shared_bytes": slots * (rows + M) * row_bytes(chunk_windows)}
+            "shared_bytes": slots * held * row_bytes(chunk_windows)}
 
 
 def grid_for(work_items: int, threads: int = 256, cap: int = SM_COUNT * 8) -> int:
@@ -274,7 +276,7 @@ class RecipeBuilder:
         # keys one block of 8 query rows can see: everything, or one diagonal block (plus alignment slack)
         span = kv_rows if mask != "block" else min(kv_rows, mask_arg * (1 + ceil_div(8, mask_arg)))
         span_pad = ceil_div(span, 32) * 32
-        smem = span * (2 * head_dim + 2) * 2 + 8 * head_dim * 4 + 8 * span_pad * 4
+        smem = span * (2 * head_dim + 2) * 2 + 16 + 8 * head_dim * 4 + 8 * span_pad * 4
         aligned = head_dim % 8 == 0 and k_stride % 8 == 0 and v_stride % 8 == 0
         if aligned and smem <= ATTN_SMEM_BUDGET and algorithm != "warp_per_row":
             self.launch("agi_attention_smem_bf16", (ceil_div(q_rows, 8), q_heads, 1), (256, 1, 1), args + [U32(span)],
@@ -349,6 +351,52 @@ class RecipeBuilder:
                     args[:7] + [partial, counters, Arena(STATUS_WORD)] + args[7:] + [U32(t["TN"]), U32(t["stages"])],
                     shared_bytes=t["shared_bytes"], op=f"gemm_{dtype}",
                     algorithm=f"tcgen05_128x{t['TN']}_s{t['stages']}_k{t['splits']}")
+
+    def fused_linear(self, x: Pointer, parts: Sequence[tuple[Pointer, Pointer | None, int]], y: Pointer, M: int, K: int,
+                     *, ln: dict[str, Any] | None = None, ln_scratch: Pointer | None = None,
+                     residual: Pointer | None = None, act: str | None = None, ldx: int | None = None,
+                     ldy: int | None = None, fuse: bool = True) -> None:
+        """``y[:, blocks] = epilogue(LN?(x) . [W0 | W1 | W2]^T)`` for bf16 and M <= 64.
+
+        ``parts``: up to three ``(weight, bias or None, N_i)``; outputs land in consecutive column blocks of
+        ``y``.  ``ln``: ``{"eps": e}`` for LayerNorm without affine, plus ``"scale"``/``"shift"`` pointers for
+        AdaLN modulation.  One launch of the fused bulk-stream kernel when the whole K range of a CTA fits one
+        ring slot; otherwise (or with ``fuse=False``) the same arithmetic as separate launches, normalising into
+        ``ln_scratch`` first."""
+        total = sum(n for _, _, n in parts)
+        ldy = ldy or total
+        t = stream_tiling(M, total, K, 2)
+        rows = t["rows"]
+        fits = (M <= 64 and (K * 2) % 64 == 0 and len(parts) <= 3 and all(n % rows == 0 for _, _, n in parts)
+                and (ln is None or (t["slots"] == 1 and ("scale" not in ln or K <= 1536)))
+                and len({b is None for _, b, _ in parts}) == 1)
+        if not (fuse and fits):
+            src = x
+            if ln is not None:
+                assert ln_scratch is not None, "fallback needs a buffer for the normalised activations"
+                self.layernorm(x, ln_scratch, M, K, ln["eps"], scale=ln.get("scale"), shift=ln.get("shift"),
+                               x_stride=ldx)
+                src, ldx = ln_scratch, None
+            col = 0
+            for w, b, n in parts:
+                self.gemm(src, w, y + col * 2 if col else y, M, n, K, bias=b, residual=(residual + col * 2 if col else
+                          residual) if residual is not None else None, act=act, ldx=ldx, ldy=ldy)
+                col += n
+            return
+        flags = ACT[act] | (FLAG_BIAS if parts[0][1] is not None else 0) | (FLAG_RESIDUAL if residual else 0)
+        if ln is not None:
+            flags |= FLAG_LAYERNORM | (FLAG_LN_MODULATE if "scale" in ln else 0)
+        dummy = Arena(0)
+        ws = [p[0] for p in parts] + [dummy] * (3 - len(parts))
+        bs = [(p[1] or dummy) for p in parts] + [dummy] * (3 - len(parts))
+        ns = [p[2] for p in parts] + [0] * (3 - len(parts))
+        tiles = next(v for v in (1, 2, 3, 4, 6, 8) if 8 * v >= M)
+        self.launch(f"agi_gemm_stream_fused_bf16_t{tiles}", (t["grid"], 1, 1), (160, 1, 1),
+                    [x, *ws, y, *bs, residual or dummy, (ln or {}).get("scale", dummy), (ln or {}).get("shift", dummy),
+                     Arena(STATUS_WORD), U32(M), *map(U32, ns), U32(K), U32(ldx or K), U32(ldy), U32(flags), U32(rows),
+                     U32(t["chunk_windows"]), F32((ln or {}).get("eps", 0.0))],
+                    shared_bytes=t["shared_bytes"], op="fused_linear_bf16",
+                    algorithm=f"bulk_stream_r{rows}_t{tiles}_x{len(parts)}" + ("_ln" if ln else ""))
 
     # ---- outputs --------------------------------------------------------------------------
     def plan(self) -> dict[str, Any]:

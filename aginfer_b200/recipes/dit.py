@@ -112,7 +112,8 @@ def synthetic_inputs(cfg: DitConfig, seed: int = 2) -> dict:
 
 
 def build_recipe(cfg: DitConfig = DitConfig(), weights: Mapping[str, tuple[str, tuple[int, ...]]] | None = None,
-                 gemm_tactic: str = "auto", profile: str = "default", stream_profile: bool = False) -> RecipeBuilder:
+                 gemm_tactic: str = "auto", profile: str = "default", stream_profile: bool = False,
+                 fuse: bool = True) -> RecipeBuilder:
     D, T, H, S = cfg.hidden, cfg.tokens, cfg.horizon, cfg.steps
     r = RecipeBuilder(weights or {k: ("BF16", v) for k, v in weight_shapes(cfg).items()})
     r.begin_profile(profile, [io("backbone_features", "BF16", [cfg.backbone_tokens, cfg.backbone_dim]),
@@ -166,8 +167,7 @@ def build_recipe(cfg: DitConfig = DitConfig(), weights: Mapping[str, tuple[str, 
     enc_cat = r.alloc(H * 2 * D * BF)     # [W1 x_t | tau(t)]
     enc_hid = r.alloc(H * D * BF)
     h = r.alloc(T * D * BF)               # normalised / modulated activations
-    q = r.alloc(T * D * BF)
-    k_self, v_self = r.alloc(T * D * BF), r.alloc(T * D * BF)
+    qkv = r.alloc(T * 3 * D * BF)         # [Q | K | V] column blocks (cross-attention blocks use the Q block only)
     attn = r.alloc(T * D * BF)
     ff = r.alloc(T * cfg.mlp * BF)
     out_hid = r.alloc(T * cfg.out_dim * BF)
@@ -188,25 +188,25 @@ def build_recipe(cfg: DitConfig = DitConfig(), weights: Mapping[str, tuple[str, 
 
         for l in range(cfg.layers):
             b = f"{P}.dit.blocks.{l}"
-            scale, shift = mods[l] + mod_row, mods[l] + (mod_row + D * BF)
-            r.layernorm(seq, h, T, D, cfg.ln_eps, scale=scale, shift=shift)
-            lin(h, f"{b}.attn.to_q", q, T, D, D)
+            adaln = {"eps": cfg.ln_eps, "scale": mods[l] + mod_row, "shift": mods[l] + (mod_row + D * BF)}
+            part = lambda name, n: (Weight(f"{b}.{name}.weight"), Weight(f"{b}.{name}.bias"), n)
             if cfg.is_cross(l):
-                k_buf, v_buf, kv_rows = (*kv[l], cfg.backbone_tokens)
+                r.fused_linear(seq, [part("attn.to_q", D)], qkv, T, D, ln=adaln, ln_scratch=h, ldy=3 * D, fuse=fuse)
+                k_buf, v_buf, kv_rows, kv_stride = (*kv[l], cfg.backbone_tokens, D)
             else:
-                lin(h, f"{b}.attn.to_k", k_self, T, D, D)
-                lin(h, f"{b}.attn.to_v", v_self, T, D, D)
-                k_buf, v_buf, kv_rows = k_self, v_self, T
-            r.attention(q, k_buf, v_buf, attn, q_rows=T, kv_rows=kv_rows, q_heads=cfg.heads, kv_heads=cfg.heads,
-                        head_dim=cfg.head_dim, q_stride=D, k_stride=D, v_stride=D, o_stride=D)
+                r.fused_linear(seq, [part("attn.to_q", D), part("attn.to_k", D), part("attn.to_v", D)], qkv, T, D,
+                               ln=adaln, ln_scratch=h, ldy=3 * D, fuse=fuse)
+                k_buf, v_buf, kv_rows, kv_stride = qkv + D * BF, qkv + 2 * D * BF, T, 3 * D
+            r.attention(qkv, k_buf, v_buf, attn, q_rows=T, kv_rows=kv_rows, q_heads=cfg.heads, kv_heads=cfg.heads,
+                        head_dim=cfg.head_dim, q_stride=3 * D, k_stride=kv_stride, v_stride=kv_stride, o_stride=D)
             lin(attn, f"{b}.attn.to_out", seq, T, D, D, residual=seq)
-            r.layernorm(seq, h, T, D, cfg.ln_eps)
-            lin(h, f"{b}.ff.fc1", ff, T, cfg.mlp, D, act="gelu_tanh")
+            r.fused_linear(seq, [part("ff.fc1", cfg.mlp)], ff, T, D, ln={"eps": cfg.ln_eps}, ln_scratch=h,
+                           act="gelu_tanh", fuse=fuse)
             lin(ff, f"{b}.ff.fc2", seq, T, D, cfg.mlp, residual=seq)
 
-        scale, shift = mods[cfg.layers] + mod_row, mods[cfg.layers] + (mod_row + D * BF)
-        r.layernorm(seq, h, T, D, cfg.ln_eps, scale=scale, shift=shift)
-        lin(h, f"{P}.dit.proj_out", out_hid, T, cfg.out_dim, D)
+        r.fused_linear(seq, [(Weight(f"{P}.dit.proj_out.weight"), Weight(f"{P}.dit.proj_out.bias"), cfg.out_dim)],
+                       out_hid, T, D, ln={"eps": cfg.ln_eps, "scale": mods[cfg.layers] + mod_row,
+                                          "shift": mods[cfg.layers] + (mod_row + D * BF)}, ln_scratch=h, fuse=fuse)
         lin(out_hid + cfg.out_dim * BF, f"{P}.action_decoder.fc1", dec_hid, H, cfg.encoder_hidden, cfg.out_dim, act="relu")
         lin(dec_hid, f"{P}.action_decoder.fc2", velocity, H, cfg.action_dim, cfg.encoder_hidden)
         elementwise("agi_euler_step", [x_f32, velocity, x_bf, F32(1.0 / S), U32(H * cfg.action_dim)],
@@ -222,12 +222,13 @@ def build_recipe(cfg: DitConfig = DitConfig(), weights: Mapping[str, tuple[str, 
         r.begin_profile("gemm_stream", [io("token", "I32", [1])], [io("status", "I32", [1])])
         for l in range(cfg.layers):
             b = f"{P}.dit.blocks.{l}"
-            lin(h, f"{b}.attn.to_q", q, T, D, D)
-            if not cfg.is_cross(l):
-                lin(h, f"{b}.attn.to_k", k_self, T, D, D)
-                lin(h, f"{b}.attn.to_v", v_self, T, D, D)
+            part = lambda name, n: (Weight(f"{b}.{name}.weight"), Weight(f"{b}.{name}.bias"), n)
+            names = ["attn.to_q"] if cfg.is_cross(l) else ["attn.to_q", "attn.to_k", "attn.to_v"]
+            r.fused_linear(seq, [part(n, D) for n in names], qkv, T, D, ln={"eps": cfg.ln_eps}, ln_scratch=h,
+                           ldy=3 * D, fuse=fuse)
             lin(attn, f"{b}.attn.to_out", seq, T, D, D, residual=seq)
-            lin(h, f"{b}.ff.fc1", ff, T, cfg.mlp, D, act="gelu_tanh")
+            r.fused_linear(seq, [part("ff.fc1", cfg.mlp)], ff, T, D, ln={"eps": cfg.ln_eps}, ln_scratch=h,
+                           act="gelu_tanh", fuse=fuse)
             lin(ff, f"{b}.ff.fc2", seq, T, D, cfg.mlp, residual=seq)
         r.export_status(Tensor("status"))
     return r
@@ -238,8 +239,7 @@ def stream_profile_bytes(cfg: DitConfig = DitConfig()) -> tuple[int, int]:
     N*K*2 (weights) + M*K*2 (activations in) + M*N*2 (out) + N*2 (bias), residual reads included."""
     D, T, total, count = cfg.hidden, cfg.tokens, 0, 0
     for l in range(cfg.layers):
-        shapes = [(D, D, False)] + ([] if cfg.is_cross(l) else [(D, D, False), (D, D, False)]) + \
-            [(D, D, True), (cfg.mlp, D, False), (D, cfg.mlp, True)]
+        shapes = [(D if cfg.is_cross(l) else 3 * D, D, False), (D, D, True), (cfg.mlp, D, False), (D, cfg.mlp, True)]
         for N, K, residual in shapes:
             total += N * K * 2 + T * K * 2 + T * N * 2 + N * 2 + (T * N * 2 if residual else 0)
             count += 1

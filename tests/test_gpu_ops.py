@@ -286,3 +286,32 @@ def test_gemm_skinny(tmp_path, case, tactic):
     got, _ = run_recipe(tmp_path, weights, inputs, {"y": (BF, (M, N)), "status": (torch.int32, (1,))}, body, repeats=2)
     assert got["status"].item() == 0, hex(got["status"].item())
     assert ops.max_rel_err(got["y"], want) < 1e-2
+
+
+@pytest.mark.parametrize("fuse", [True, False], ids=["one_launch", "separate_launches"])
+@pytest.mark.parametrize("modulated", [True, False])
+def test_fused_layernorm_qkv_linear(tmp_path, fuse, modulated):
+    # AdaLN + Q|K|V projections of the action head as one launch, against LN -> three GEMMs in the oracle
+    M, K, N = 17, 1536, 1536
+    x = (randn(M, K, seed=41).float() * 2 + 0.5).to(BF)
+    ws = [randn(N, K, seed=42 + i, std=0.02) for i in range(3)]
+    bs = [randn(N, seed=45 + i, std=0.1) for i in range(3)]
+    mod = randn(2 * K, seed=48, std=0.3)
+    weights = {f"w{i}": ws[i] for i in range(3)} | {f"b{i}": bs[i] for i in range(3)} | {"mod": mod}
+
+    def body(r):
+        scratch = r.alloc(M * K * 2)
+        ln = {"eps": 1e-5}
+        if modulated:
+            ln |= {"scale": Weight("mod"), "shift": Weight("mod") + 2 * K}
+        r.fused_linear(Tensor("x"), [(Weight(f"w{i}"), Weight(f"b{i}"), N) for i in range(3)], Tensor("y"), M, K,
+                       ln=ln, ln_scratch=scratch, fuse=fuse)
+        r.export_status(Tensor("status"))
+
+    got, stats = run_recipe(tmp_path, weights, {"x": x}, {"y": (BF, (M, 3 * N)), "status": (torch.int32, (1,))}, body,
+                            repeats=2)
+    assert got["status"].item() == 0
+    assert stats["launches_per_enqueue"] == (3 if fuse else 6)
+    h = ops.layernorm(x, 1e-5, mod[:K], mod[K:]) if modulated else ops.layernorm(x, 1e-5)
+    want = torch.cat([ops.gemm(h, ws[i], bias=bs[i]) for i in range(3)], dim=1)
+    assert ops.max_rel_err(got["y"], want) < 1e-2
