@@ -27,10 +27,20 @@
 #include "gemm_simt.cuh"    // gemm_store
 #include "gemm_skinny.cuh"  // mma16n8
 
+// Phase tracing for kernel tuning: with -DAGI_TRACE, CTA 0 stores SM clock stamps into the status area
+// (words 32..47: producer lane, words 48..63: consumer warp 0).  Compiled out of the shipped bundle.
+#ifdef AGI_TRACE
+#define AGI_STAMP(slot) do { if (blockIdx.x == 0 && lane == 0) status[(slot)] = (unsigned)clock64(); } while (0)
+#else
+#define AGI_STAMP(slot) do { } while (0)
+#endif
+
 namespace stream {
 
-constexpr int kConsumerWarps = 4;
-constexpr int kThreads = (kConsumerWarps + 1) * 32;  // + one producer warp
+// Consumer warps per CTA (plus one producer warp).  Four: the MMA phase is bound by the warp-level MMA
+// issue rate of the SM, not by the number of warps, and small CTAs let several share an SM.
+__host__ __device__ constexpr int consumer_warps(int) { return 4; }
+__host__ __device__ constexpr int threads(int token_tiles) { return (consumer_warps(token_tiles) + 1) * 32; }
 constexpr int kSlots = 2;
 constexpr unsigned kSpinLimit = 1u << 22;
 constexpr unsigned kTimeoutFull = 0x400, kTimeoutEmpty = 0x500;
@@ -84,15 +94,17 @@ struct Extra {
   float ln_eps = 0.f;
 };
 
-template <bool kFp8, int NT>
+template <bool kFp8, int NT, bool kLn = false>
 __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y, const bf16* bias,
                                      const bf16* residual, const float* scale_a, const float* scale_w,
                                      unsigned* status, unsigned M, unsigned N, unsigned K, unsigned ldx, unsigned ldy,
                                      unsigned flags, unsigned rows, unsigned chunk_windows, const Extra extra = Extra()) {
-  extern __shared__ __align__(128) unsigned char ring[];  // kSlots x (rows + M) x (chunk bytes + 16)
+  AGI_TRACE_KERNEL(kLn ? 6 : 5);
+  constexpr int kConsumerWarps = consumer_warps(NT);
+  constexpr int kThreads = threads(NT);
+  // dynamic shared memory: ring of slots (rows + M rows each), then the warps' partial tiles
+  extern __shared__ __align__(128) unsigned char ring[];
   __shared__ __align__(8) unsigned long long full_bar[kSlots], empty_bar[kSlots];
-  constexpr int kPitch = NT * 8 + 1;
-  __shared__ float partial[kConsumerWarps][16][kPitch];
 
   const unsigned elem = kFp8 ? 1u : 2u;
   const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
@@ -100,10 +112,17 @@ __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y
   const unsigned k_bytes = K * elem;
   const unsigned windows = k_bytes / 64;
   const unsigned chunks = (windows + chunk_windows - 1) / chunk_windows;
-  const unsigned pitch = chunk_windows * 64 + 16;
+  // Slab mode: K is one chunk and both operands are contiguous in global memory, so each arrives with a
+  // single bulk copy into unpadded rows (fragment reads then take twice the shared-memory wavefronts,
+  // which is cheap; issuing dozens of small bulk copies is not).
+  const bool slab = (flags & kFlagSlab) != 0;
+  const unsigned pitch = chunk_windows * 64 + (slab ? 0u : 16u);
   constexpr unsigned mod_rows = 0;
   const unsigned slot_bytes = (rows + M + mod_rows) * pitch;
   const unsigned ring_base = smem_u32(ring);
+  const unsigned ring_slots = chunks < unsigned(kSlots) ? chunks : unsigned(kSlots);
+  const unsigned mp = M | 1u;  // odd pitch of a partial-tile row: rows land in different banks
+  float* partial = reinterpret_cast<float*>(ring + ((ring_slots * slot_bytes + 15u) & ~15u));  // [warp][16][mp]
   // Which of the side-by-side weight matrices this CTA's rows belong to.
   unsigned seg_rows = N, local0 = row0, col0 = 0;
   const uint8_t* w_seg = w;
@@ -125,10 +144,27 @@ __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y
   }
   __syncthreads();
 
+  // Each thread's first output element (i = threadIdx.x): its bias and residual are fetched early, as soon
+  // as the previous kernel's results are known to be visible, and used after the reduction.
+  float early_bias = 0.f, early_residual = 0.f;
+  bool early_valid = false;
+  auto fetch_early = [&]() {
+    const unsigned i = threadIdx.x;
+    if (i < rows * M) {
+      const unsigned r = i % rows, m = i / rows;
+      if (local0 + r < seg_rows) {
+        const unsigned n = col0 + local0 + r;
+        if (flags & kFlagBias) early_bias = __bfloat162float(bias_seg[local0 + r]);
+        if (flags & kFlagResidual) early_residual = __bfloat162float(residual[size_t(m) * ldy + n]);
+        early_valid = true;
+      }
+    }
+  };
   if (warp == kConsumerWarps) {
     // ---------------- producer warp ----------------
     const size_t x_row = size_t(ldx) * elem;
     bool waited = false;
+    AGI_STAMP(32);
     for (unsigned c = 0; c < chunks; ++c) {
       const unsigned slot = c % kSlots, round = c / kSlots;
       const unsigned first = c * chunk_windows, count = min(chunk_windows, windows - first);
@@ -136,18 +172,27 @@ __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y
       const unsigned base = ring_base + slot * slot_bytes;
       const unsigned bar = smem_u32(&full_bar[slot]);
       if (round > 0) bounded_wait(smem_u32(&empty_bar[slot]), (round - 1) & 1, status, kTimeoutEmpty | slot);
-      if (lane == 0) expect_bytes(bar, bytes * (rows + M + mod_rows));
+      const unsigned live_rows = min(rows, seg_rows - local0);
+      if (lane == 0) expect_bytes(bar, bytes * ((slab ? live_rows : rows) + M + mod_rows));
       __syncwarp();
+      if (slab) {
+        if (lane == 0) bulk_copy(base, w_seg + size_t(local0) * k_bytes, bytes * live_rows, bar);
+      } else
       for (unsigned r = lane; r < rows; r += 32)  // rows past N re-read the last row; their results are dropped
         bulk_copy(base + r * pitch, w_seg + size_t(min(local0 + r, seg_rows - 1)) * k_bytes + size_t(first) * 64, bytes, bar);
       if (!waited && (c + 1 == kSlots || c + 1 == chunks)) {
         // The weight copies of the first slots are in flight; only now wait for the previous kernel,
         // then fetch the activations it produced for those slots.
+        AGI_STAMP(33);
         grid_dependency_wait();
+        AGI_STAMP(34);
         waited = true;
         for (unsigned cc = 0; cc <= c; ++cc) {
           const unsigned f = cc * chunk_windows, n = min(chunk_windows, windows - f);
           const unsigned b2 = ring_base + (cc % kSlots) * slot_bytes + rows * pitch;
+          if (slab) {
+            if (lane == 0) bulk_copy(b2, x, n * 64 * M, smem_u32(&full_bar[cc % kSlots]));
+          } else
           for (unsigned m = lane; m < M; m += 32)
             bulk_copy(b2 + m * pitch, x + m * x_row + size_t(f) * 64, n * 64, smem_u32(&full_bar[cc % kSlots]));
         }
@@ -157,17 +202,24 @@ __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y
       }
     }
     if (!waited) grid_dependency_wait();
+    fetch_early();
+    AGI_STAMP(35);
   } else {
     // ---------------- consumer warps ----------------
-    float acc[NT][4];
+    // Two accumulator sets (one per MMA of a 16-byte chunk) keep consecutive MMAs independent; fragments
+    // of the next window are read from shared memory while the current window multiplies.
+    float acc[2][NT][4];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
+    for (int h2 = 0; h2 < 2; ++h2)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[h2][nt][i] = 0.f;
     const bool two_halves = rows == 16;
     unsigned b_off[NT];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) b_off[nt] = (rows + min(unsigned(nt * 8) + g, M - 1)) * pitch + t * 16;
+    uint4 fa_lo[2], fa_hi[2], fb[2][NT];
     for (unsigned c = 0; c < chunks; ++c) {
       const unsigned slot = c % kSlots, round = c / kSlots;
       const unsigned count = min(chunk_windows, windows - c * chunk_windows);
@@ -175,7 +227,7 @@ __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y
       // AdaLN vectors (one value per column, up to 6 x 8 columns per lane: K <= 1536) are fetched from global
       // memory while the slot is still filling.
       Bf16x8 mod_scale[6], mod_shift[6];
-      if (!kFp8 && (flags & kFlagLnModulate) && c == 0) {
+      if (kLn && (flags & kFlagLnModulate) && c == 0) {
 #pragma unroll
         for (int i = 0; i < 6; ++i) {
           const unsigned v = lane + 32 * i;
@@ -185,101 +237,140 @@ __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y
           }
         }
       }
+      if (warp == 0 && c == 0) AGI_STAMP(48);
       bounded_wait(smem_u32(&full_bar[slot]), round & 1, status, kTimeoutFull | slot);
-      if (!kFp8 && (flags & kFlagLayerNorm) && c == 0) {
+      if (warp == 0 && c == 0) AGI_STAMP(49);
+      if (c == 0) fetch_early();  // the slot landed, so the producer has passed the grid-dependency wait
+      if (kLn && (flags & kFlagLayerNorm) && c == 0) {
         // Fused LayerNorm (whole rows are in this slot: the recipe only sets the flag when K is one chunk).
-        // Warp w normalises rows w, w + 4, ... in place, rounding to bf16 exactly where the stand-alone
-        // kernel would have stored them; then the four consumer warps meet before anyone multiplies.
+        // Warp w normalises rows w, w + W, ... in place, rounding to bf16 exactly where the stand-alone
+        // kernel would have stored them; then the consumer warps meet before anyone multiplies.
         unsigned char* slot_ptr = ring + slot * slot_bytes;
         const unsigned vecs = K / 8;
         for (unsigned m = warp; m < M; m += kConsumerWarps) {
           Bf16x8* xr = reinterpret_cast<Bf16x8*>(slot_ptr + (rows + m) * pitch);
+          // the row (up to 6 x 8 values per lane, K <= 1536) stays in registers across the three passes
+          float f[6][8];
           float sum = 0.f;
-          for (unsigned i = lane; i < vecs; i += 32) {
-            float f[8];
-            unpack8(xr[i], f);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) sum += f[j];
+          for (int q = 0; q < 6; ++q) {
+            const unsigned i = lane + 32 * q;
+            if (i < vecs) {
+              unpack8(xr[i], f[q]);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) sum += f[q][j];
+            }
           }
           const float mean = warp_sum(sum) / float(K);
           float var = 0.f;
-          for (unsigned i = lane; i < vecs; i += 32) {
-            float f[8];
-            unpack8(xr[i], f);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) var += (f[j] - mean) * (f[j] - mean);
-          }
+          for (int q = 0; q < 6; ++q)
+            if (lane + 32 * q < vecs) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) var += (f[q][j] - mean) * (f[q][j] - mean);
+            }
           const float rstd = rsqrtf(warp_sum(var) / float(K) + extra.ln_eps);
-          if (flags & kFlagLnModulate) {
 #pragma unroll
-            for (int q = 0; q < 6; ++q) {
-              const unsigned i = lane + 32 * q;
-              if (i < vecs) {
-                float f[8], a[8], b[8];
-                unpack8(xr[i], f);
+          for (int q = 0; q < 6; ++q) {
+            const unsigned i = lane + 32 * q;
+            if (i < vecs) {
+              if (flags & kFlagLnModulate) {
+                float a[8], b[8];
                 unpack8(mod_scale[q], a);
                 unpack8(mod_shift[q], b);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) f[j] = (f[j] - mean) * rstd * (1.f + a[j]) + b[j];
-                xr[i] = pack8(f);
-              }
-            }
-          } else {
-            for (unsigned i = lane; i < vecs; i += 32) {
-              float f[8];
-              unpack8(xr[i], f);
+                for (int j = 0; j < 8; ++j) f[q][j] = (f[q][j] - mean) * rstd * (1.f + a[j]) + b[j];
+              } else {
 #pragma unroll
-              for (int j = 0; j < 8; ++j) f[j] = (f[j] - mean) * rstd;
-              xr[i] = pack8(f);
+                for (int j = 0; j < 8; ++j) f[q][j] = (f[q][j] - mean) * rstd;
+              }
+              xr[i] = pack8(f[q]);
             }
           }
         }
         asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
       }
+      if (warp == 0 && c == 0) AGI_STAMP(50);
       const unsigned a_lo = base + g * pitch + t * 16, a_hi = a_lo + 8 * pitch;
-      for (unsigned win = warp; win < count; win += kConsumerWarps) {
-        const uint4 lo = lds128(a_lo + win * 64);
-        const uint4 hi = two_halves ? lds128(a_hi + win * 64) : make_uint4(0, 0, 0, 0);
+      auto fetch = [&](int buf, unsigned win) {
+        fa_lo[buf] = lds128(a_lo + win * 64);
+        fa_hi[buf] = two_halves ? lds128(a_hi + win * 64) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) fb[buf][nt] = lds128(base + b_off[nt] + win * 64);
+      };
+      auto multiply = [&](int buf) {
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-          const uint4 b = lds128(base + b_off[nt] + win * 64);
-          skinny::mma16n8<kFp8>(acc[nt], lo.x, hi.x, lo.y, hi.y, b.x, b.y);
-          skinny::mma16n8<kFp8>(acc[nt], lo.z, hi.z, lo.w, hi.w, b.z, b.w);
+          skinny::mma16n8<kFp8>(acc[0][nt], fa_lo[buf].x, fa_hi[buf].x, fa_lo[buf].y, fa_hi[buf].y, fb[buf][nt].x, fb[buf][nt].y);
+          skinny::mma16n8<kFp8>(acc[1][nt], fa_lo[buf].z, fa_hi[buf].z, fa_lo[buf].w, fa_hi[buf].w, fb[buf][nt].z, fb[buf][nt].w);
         }
+      };
+      unsigned win = warp;
+      if (win < count) fetch(0, win);
+      while (win < count) {
+        unsigned next = win + kConsumerWarps;
+        if (next < count) fetch(1, next);
+        multiply(0);
+        win = next;
+        if (win >= count) break;
+        next = win + kConsumerWarps;
+        if (next < count) fetch(0, next);
+        multiply(1);
+        win = next;
       }
       __syncwarp();
       if (lane == 0 && c + kSlots < chunks) arrive(smem_u32(&empty_bar[slot]));
     }
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-      partial[warp][g][nt * 8 + 2 * t] = acc[nt][0];
-      partial[warp][g][nt * 8 + 2 * t + 1] = acc[nt][1];
-      partial[warp][g + 8][nt * 8 + 2 * t] = acc[nt][2];
-      partial[warp][g + 8][nt * 8 + 2 * t + 1] = acc[nt][3];
+      float* tile = partial + size_t(warp) * 16 * mp;
+      const unsigned col = nt * 8 + 2 * t;  // columns past M are padding of the token tile: not stored
+      if (col < M) {
+        tile[g * mp + col] = acc[0][nt][0] + acc[1][nt][0];
+        tile[(g + 8) * mp + col] = acc[0][nt][2] + acc[1][nt][2];
+      }
+      if (col + 1 < M) {
+        tile[g * mp + col + 1] = acc[0][nt][1] + acc[1][nt][1];
+        tile[(g + 8) * mp + col + 1] = acc[0][nt][3] + acc[1][nt][3];
+      }
     }
   }
+  if (warp == 0) AGI_STAMP(51);
   grid_dependency_release();
   __syncthreads();
+  if (warp == 0) AGI_STAMP(52);
   const float alpha = (flags & kFlagScaled) ? (*scale_a) * (*scale_w) : 1.f;
   for (unsigned i = threadIdx.x; i < rows * M; i += kThreads) {
     const unsigned r = i % rows, m = i / rows;
     if (local0 + r >= seg_rows) continue;
     float total = 0.f;
 #pragma unroll
-    for (int wq = 0; wq < kConsumerWarps; ++wq) total += partial[wq][r][m];
+    for (int wq = 0; wq < kConsumerWarps; ++wq) total += partial[(wq * 16 + r) * mp + m];
     // bias is indexed inside its own matrix, the output column across all of them
     const unsigned n = col0 + local0 + r;
-    gemm_store(total, m, n, y, ldy, bias_seg - col0, residual, alpha, flags);
+    if (i == threadIdx.x && early_valid) {
+      // first output of this thread: bias and residual were fetched while the MMAs ran
+      float v = total * alpha;
+      if (flags & kFlagBias) v += early_bias;
+      v = apply_activation(v, flags);
+      if (flags & kFlagResidual) v += early_residual;
+      if (flags & kFlagOutF32) static_cast<float*>(y)[size_t(m) * ldy + n] = v;
+      else static_cast<bf16*>(y)[size_t(m) * ldy + n] = __float2bfloat16_rn(v);
+    } else {
+      gemm_store(total, m, n, y, ldy, bias_seg - col0, residual, alpha, flags);
+    }
   }
+  if (warp == 0) AGI_STAMP(53);
 }
 
 }  // namespace stream
 
-// grid = (ceil(N / rows), 1, 1), block = 160,
-// dynamic shared memory = min(2, chunks) * (rows + M) * (chunk_windows * 64 + 16);
+// grid = (ceil(N / rows), 1, 1), block = 288 threads for up to 32 tokens, 160 above,
+// dynamic shared memory = min(2, chunks) * (rows + M) * pitch + 16 + warps * 16 * (M | 1) * 4,
+// pitch = chunk_windows * 64 (+ 16 unless the slab flag is set);
 // M <= 8 * tiles; K bytes a multiple of 64; rows in {8, 16}.
 #define AGI_STREAM_KERNEL(NAME, TYPE, FP8, NT)                                                                       \
-  extern "C" __global__ void __launch_bounds__(stream::kThreads)                                                     \
+  extern "C" __global__ void __launch_bounds__(stream::threads(NT), NT <= 4 ? 3 : 1)                                                  \
   NAME(const TYPE* x, const TYPE* w, void* y, const bf16* bias, const bf16* residual, const float* scale_a,         \
        const float* scale_w, unsigned* status, unsigned M, unsigned N, unsigned K, unsigned ldx, unsigned ldy,      \
        unsigned flags, unsigned rows, unsigned chunk_windows) {                                                             \
@@ -287,11 +378,11 @@ __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y
                           residual, scale_a, scale_w, status, M, N, K, ldx, ldy, flags, rows, chunk_windows);       \
   }
 
-// The fused bf16 family: up to three weight matrices side by side along N (N0 | N1 | N2, zeros when unused)
-// and an optional LayerNorm / AdaLN prologue over the activation rows (flags kFlagLayerNorm, kFlagLnModulate;
+// The fused bf16 families: up to three weight matrices side by side along N (N0 | N1 | N2, zeros when unused);
+// the `lnfused` kernels add an optional LayerNorm / AdaLN prologue over the activation rows (flags kFlagLayerNorm, kFlagLnModulate;
 // needs K in one chunk, and K <= 1536 when modulating).
-#define AGI_STREAM_FUSED_KERNEL(NAME, NT)                                                                            \
-  extern "C" __global__ void __launch_bounds__(stream::kThreads)                                                     \
+#define AGI_STREAM_FUSED_KERNEL(NAME, NT, LN)                                                                          \
+  extern "C" __global__ void __launch_bounds__(stream::threads(NT), NT <= 4 ? 3 : 1)                                                  \
   NAME(const bf16* x, const bf16* w0, const bf16* w1, const bf16* w2, void* y, const bf16* bias0, const bf16* bias1, \
        const bf16* bias2, const bf16* residual, const bf16* ln_scale, const bf16* ln_shift, unsigned* status,        \
        unsigned M, unsigned N0, unsigned N1, unsigned N2, unsigned K, unsigned ldx, unsigned ldy, unsigned flags,    \
@@ -306,17 +397,23 @@ __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y
     extra.ln_scale = ln_scale;                                                                                       \
     extra.ln_shift = ln_shift;                                                                                       \
     extra.ln_eps = ln_eps;                                                                                           \
-    stream::body<false, NT>(reinterpret_cast<const uint8_t*>(x), reinterpret_cast<const uint8_t*>(w0), y, bias0,     \
+    stream::body<false, NT, LN>(reinterpret_cast<const uint8_t*>(x), reinterpret_cast<const uint8_t*>(w0), y, bias0, \
                             residual, nullptr, nullptr, status, M, N0, K, ldx, ldy, flags, rows, chunk_windows,     \
                             extra);                                                                                  \
   }
 
-AGI_STREAM_FUSED_KERNEL(agi_gemm_stream_fused_bf16_t1, 1)
-AGI_STREAM_FUSED_KERNEL(agi_gemm_stream_fused_bf16_t2, 2)
-AGI_STREAM_FUSED_KERNEL(agi_gemm_stream_fused_bf16_t3, 3)
-AGI_STREAM_FUSED_KERNEL(agi_gemm_stream_fused_bf16_t4, 4)
-AGI_STREAM_FUSED_KERNEL(agi_gemm_stream_fused_bf16_t6, 6)
-AGI_STREAM_FUSED_KERNEL(agi_gemm_stream_fused_bf16_t8, 8)
+AGI_STREAM_FUSED_KERNEL(agi_gemm_stream_fused_bf16_t1, 1, false)
+AGI_STREAM_FUSED_KERNEL(agi_gemm_stream_lnfused_bf16_t1, 1, true)
+AGI_STREAM_FUSED_KERNEL(agi_gemm_stream_fused_bf16_t2, 2, false)
+AGI_STREAM_FUSED_KERNEL(agi_gemm_stream_lnfused_bf16_t2, 2, true)
+AGI_STREAM_FUSED_KERNEL(agi_gemm_stream_fused_bf16_t3, 3, false)
+AGI_STREAM_FUSED_KERNEL(agi_gemm_stream_lnfused_bf16_t3, 3, true)
+AGI_STREAM_FUSED_KERNEL(agi_gemm_stream_fused_bf16_t4, 4, false)
+AGI_STREAM_FUSED_KERNEL(agi_gemm_stream_lnfused_bf16_t4, 4, true)
+AGI_STREAM_FUSED_KERNEL(agi_gemm_stream_fused_bf16_t6, 6, false)
+AGI_STREAM_FUSED_KERNEL(agi_gemm_stream_lnfused_bf16_t6, 6, true)
+AGI_STREAM_FUSED_KERNEL(agi_gemm_stream_fused_bf16_t8, 8, false)
+AGI_STREAM_FUSED_KERNEL(agi_gemm_stream_lnfused_bf16_t8, 8, true)
 #undef AGI_STREAM_FUSED_KERNEL
 
 AGI_STREAM_KERNEL(agi_gemm_stream_bf16_t1, bf16, false, 1)

@@ -28,6 +28,12 @@
 #include "common.cuh"
 #include "gemm_simt.cuh"  // gemm_store
 
+#ifdef AGI_TRACE
+#define TC_STAMP(slot) do { if (blockIdx.x == 0 && blockIdx.z == 0 && lane == 0) status[(slot)] = (unsigned)clock64(); } while (0)
+#else
+#define TC_STAMP(slot) do { } while (0)
+#endif
+
 namespace tc {
 
 constexpr unsigned kTileN = 128;          // weight rows per CTA (MMA M)
@@ -132,6 +138,21 @@ __device__ __forceinline__ void tmem_load16(unsigned addr, float v[16]) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// Thread-block cluster helpers (split-K slices of one output tile form a cluster along grid z).
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of `local_smem_addr` in the shared memory of cluster rank `rank`.
+__device__ __forceinline__ unsigned peer_smem(unsigned local_smem_addr, unsigned rank) {
+  unsigned remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ void store_peer_f32(unsigned remote_addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote_addr), "f"(v) : "memory");
+}
+
 __device__ __forceinline__ unsigned tmem_columns_for(unsigned tokens) {
   unsigned c = 32;
   while (c < tokens) c <<= 1;
@@ -140,12 +161,13 @@ __device__ __forceinline__ unsigned tmem_columns_for(unsigned tokens) {
 
 // grid = (ceil(N / 128), ceil(M / TN), splits), block = 160 threads,
 // dynamic shared memory = stages * (16384 + TN * 128) + 1024.
-template <bool kFp8>
+template <bool kFp8, int kCluster = 1>
 __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, void* y, const bf16* bias,
                                           const bf16* residual, const float* scale_a, const float* scale_w,
                                           float* partial, unsigned* counters, unsigned* status, unsigned M,
                                           unsigned N, unsigned K, unsigned ldx, unsigned ldy, unsigned flags,
-                                          unsigned TN, unsigned stages) {
+                                          unsigned TN, unsigned stages, unsigned tile_x = 0xffffffffu) {
+  AGI_TRACE_KERNEL(kCluster > 1 ? 8 : 7);
   extern __shared__ unsigned char dynamic_smem[];
   __shared__ __align__(8) unsigned long long full_bar[kMaxStages];
   __shared__ __align__(8) unsigned long long empty_bar[kMaxStages];
@@ -155,7 +177,8 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
 
   const unsigned tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const unsigned elem = kFp8 ? 1u : 2u;
-  const unsigned n0 = blockIdx.x * kTileN, m0 = blockIdx.y * TN;
+  if (tile_x == 0xffffffffu) tile_x = blockIdx.x;  // batched launches pass the tile index inside their matrix
+  const unsigned n0 = tile_x * kTileN, m0 = blockIdx.y * TN;
   const unsigned splits = gridDim.z, split = blockIdx.z;
   const unsigned k_blocks_total = (K * elem) / kRowBytes;
   const unsigned per_split = (k_blocks_total + splits - 1) / splits;
@@ -165,9 +188,13 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
   const unsigned stage_bytes = kATileBytes + TN * kRowBytes;
   const unsigned ring = (smem_u32(dynamic_smem) + 1023u) & ~1023u;  // tiles need 1024-byte alignment
   const unsigned columns = tmem_columns_for(TN);
+  // Cluster mode: [slice][token / kCluster][128 rows] fp32 gather buffer behind the ring.
+  const unsigned gather_cols = (TN + kCluster - 1) / kCluster;
+  const unsigned gather_base = ring + stages * stage_bytes;
   const unsigned Np = gridDim.x * kTileN;  // row stride of the split-K slabs: N rounded up to whole tiles
   if (stages > kMaxStages) stages = kMaxStages;
 
+  if (warp == 0) TC_STAMP(32);
   if (tid == 0) {
     for (unsigned s = 0; s < stages; ++s) {
       mbar_init(&full_bar[s], kProducers);
@@ -181,9 +208,14 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
   __syncthreads();
   tc_fence_after();
   const unsigned tmem_base = tmem_slot;
+  // Cluster split-K: every slice must be running (its shared memory live) before anyone writes into it.
+  if (warp == 0) TC_STAMP(33);
+  if (kCluster > 1) cluster_sync();
+  if (warp == 0) TC_STAMP(34);
 
   grid_dependency_wait();
   grid_dependency_release();
+  if (warp == 0) TC_STAMP(35);
 
   if (warp < 4) {
     // ---------------- producers ----------------
@@ -236,8 +268,10 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
   }
 
   // ---------------- epilogue (warps 0-3: TMEM lanes 32 * warp ... +31) ----------------
+  if (warp == 0) TC_STAMP(36);   // producer loop finished
   if (warp < 4) {
     if (nkb > 0) mbar_wait(&accum_bar, 0, status, kTimeoutAccum);
+    if (warp == 0) TC_STAMP(37); // accumulator complete
     tc_fence_after();
     const unsigned n = n0 + warp * 32 + lane;
     const float alpha = (flags & kFlagScaled) ? (*scale_a) * (*scale_w) : 1.f;
@@ -255,18 +289,43 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
         for (int i = 0; i < 16; ++i) {
           const unsigned m = m0 + c0 + i;
           if (m >= M) continue;
-          if (splits == 1) gemm_store(v[i], m, n, y, ldy, bias, residual, alpha, flags);
+          if (kCluster > 1) {
+            // token m is finished by cluster rank m % kCluster: send it this slice's partial sum,
+            // filed under [this rank][m / kCluster][row of W]
+            const unsigned c = c0 + i, owner = c % kCluster;
+            const unsigned cell = gather_base + (((split * gather_cols) + c / kCluster) * kTileN + warp * 32 + lane) * 4;
+            store_peer_f32(peer_smem(cell, owner), v[i]);
+          } else if (splits == 1) gemm_store(v[i], m, n, y, ldy, bias, residual, alpha, flags);
           else __stcg(partial + (size_t(split) * M + m) * Np + n, v[i]);
         }
       }
     }
-    if (splits > 1) __threadfence();  // partial sums ordered before this CTA's arrival count
+    if (kCluster == 1 && splits > 1) __threadfence();  // partial sums ordered before this CTA's arrival count
     tc_fence_before();
+    if (warp == 0) TC_STAMP(38); // partial sums sent / stored
   }
   __syncthreads();
   if (warp == 4) {
     tc_fence_after();
     tmem_free(tmem_base, columns);
+  }
+  if (kCluster > 1) {
+    // ---------------- split-K inside a cluster: partial sums travelled through distributed shared memory ----
+    cluster_sync();  // every slice's stores into this CTA's gather buffer are complete and visible
+    if (warp == 0) TC_STAMP(39);
+    if (warp < 4) {
+      const unsigned n = n0 + warp * 32 + lane;
+      const float alpha = (flags & kFlagScaled) ? (*scale_a) * (*scale_w) : 1.f;
+      const float* mine = reinterpret_cast<const float*>(dynamic_smem + (gather_base - smem_u32(dynamic_smem)));
+      for (unsigned j = 0; split + j * kCluster < min(TN, M - m0); ++j) {  // this rank's tokens: split, split + C, ...
+        float total = 0.f;
+#pragma unroll
+        for (int z = 0; z < kCluster; ++z) total += mine[((z * gather_cols) + j) * kTileN + warp * 32 + lane];  // slice order
+        if (n < N) gemm_store(total, m0 + split + j * kCluster, n, y, ldy, bias, residual, alpha, flags);
+      }
+    }
+    if (warp == 0) TC_STAMP(40);
+    return;
   }
   if (splits == 1) return;
 
@@ -310,6 +369,56 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
 }
 
 }  // namespace tc
+
+// Cluster split-K variants: grid.z = cluster size = number of K slices (2, 3, 4, 6 or 8); partial sums are
+// exchanged through distributed shared memory, so `partial` and `counters` are unused.  For up to 64 tokens.
+// Dynamic shared memory = stages * (16384 + TN * 128) + 1024 + C * ceil(TN / C) * 512.
+#define AGI_TC_CLUSTER_KERNEL(NAME, TYPE, FP8, C)                                                                     \
+  extern "C" __global__ void __cluster_dims__(1, 1, C) __launch_bounds__(tc::kThreads, 1)                            \
+  NAME(const TYPE* x, const TYPE* w, void* y, const bf16* bias, const bf16* residual, const float* scale_a,         \
+       const float* scale_w, float* partial, unsigned* counters, unsigned* status, unsigned M, unsigned N,          \
+       unsigned K, unsigned ldx, unsigned ldy, unsigned flags, unsigned TN, unsigned stages) {                      \
+    tc::gemm_body<FP8, C>(reinterpret_cast<const uint8_t*>(x), reinterpret_cast<const uint8_t*>(w), y, bias,         \
+                          residual, scale_a, scale_w, partial, counters, status, M, N, K, ldx, ldy, flags, TN,      \
+                          stages);                                                                                   \
+  }
+AGI_TC_CLUSTER_KERNEL(agi_gemm_tc_bf16_c2, bf16, false, 2)
+AGI_TC_CLUSTER_KERNEL(agi_gemm_tc_bf16_c3, bf16, false, 3)
+AGI_TC_CLUSTER_KERNEL(agi_gemm_tc_bf16_c4, bf16, false, 4)
+AGI_TC_CLUSTER_KERNEL(agi_gemm_tc_bf16_c6, bf16, false, 6)
+AGI_TC_CLUSTER_KERNEL(agi_gemm_tc_bf16_c8, bf16, false, 8)
+AGI_TC_CLUSTER_KERNEL(agi_gemm_tc_e4m3_c2, uint8_t, true, 2)
+AGI_TC_CLUSTER_KERNEL(agi_gemm_tc_e4m3_c4, uint8_t, true, 4)
+AGI_TC_CLUSTER_KERNEL(agi_gemm_tc_e4m3_c8, uint8_t, true, 8)
+#undef AGI_TC_CLUSTER_KERNEL
+
+// Up to 16 independent GEMMs that share the activation matrix (e.g. the K and V projections of every
+// cross-attention block over the same context tokens) as ONE launch: grid.x = segments * ceil(N / 128);
+// segment s multiplies by w[s], adds bias[s] and writes y + s * seg_stride elements.  No split-K.
+extern "C" __global__ void __launch_bounds__(tc::kThreads, 1)
+agi_gemm_tc_bf16_x16(const bf16* x, void* y, unsigned* status, unsigned M, unsigned N, unsigned K, unsigned ldx,
+                     unsigned ldy, unsigned flags, unsigned TN, unsigned stages, unsigned seg_stride,
+                     const bf16* w0, const bf16* w1, const bf16* w2, const bf16* w3, const bf16* w4, const bf16* w5,
+                     const bf16* w6, const bf16* w7, const bf16* w8, const bf16* w9, const bf16* w10,
+                     const bf16* w11, const bf16* w12, const bf16* w13, const bf16* w14, const bf16* w15,
+                     const bf16* b0, const bf16* b1, const bf16* b2, const bf16* b3, const bf16* b4, const bf16* b5,
+                     const bf16* b6, const bf16* b7, const bf16* b8, const bf16* b9, const bf16* b10,
+                     const bf16* b11, const bf16* b12, const bf16* b13, const bf16* b14, const bf16* b15) {
+  const unsigned tiles = (N + tc::kTileN - 1) / tc::kTileN;
+  const unsigned seg = blockIdx.x / tiles;
+  const bf16 *w, *b;
+  switch (seg) {
+    case 0: w = w0; b = b0; break;    case 1: w = w1; b = b1; break;    case 2: w = w2; b = b2; break;
+    case 3: w = w3; b = b3; break;    case 4: w = w4; b = b4; break;    case 5: w = w5; b = b5; break;
+    case 6: w = w6; b = b6; break;    case 7: w = w7; b = b7; break;    case 8: w = w8; b = b8; break;
+    case 9: w = w9; b = b9; break;    case 10: w = w10; b = b10; break; case 11: w = w11; b = b11; break;
+    case 12: w = w12; b = b12; break; case 13: w = w13; b = b13; break; case 14: w = w14; b = b14; break;
+    default: w = w15; b = b15; break;
+  }
+  tc::gemm_body<false>(reinterpret_cast<const uint8_t*>(x), reinterpret_cast<const uint8_t*>(w),
+                       static_cast<bf16*>(y) + size_t(seg) * seg_stride, b, b, nullptr, nullptr, nullptr, nullptr, status,
+                       M, N, K, ldx, ldy, flags, TN, stages, blockIdx.x % tiles);
+}
 
 extern "C" __global__ void __launch_bounds__(tc::kThreads, 1)
 agi_gemm_tc_bf16(const bf16* x, const bf16* w, void* y, const bf16* bias, const bf16* residual, const float* scale_a,

@@ -7,6 +7,7 @@
 // One block per row, `cols` a multiple of 8.  y = bf16(x * rsqrt(mean(x^2) + eps) * gain).
 extern "C" __global__ void agi_rmsnorm_bf16(const bf16* x, const bf16* gain, bf16* y, unsigned rows, unsigned cols,
                                              unsigned x_stride, unsigned y_stride, float eps) {
+  AGI_TRACE_KERNEL(2);
   __shared__ float scratch[32];
   grid_dependency_wait();
   const unsigned row = blockIdx.x;
@@ -39,6 +40,7 @@ extern "C" __global__ void agi_rmsnorm_bf16(const bf16* x, const bf16* gain, bf1
 extern "C" __global__ void agi_layernorm_bf16(const bf16* x, const bf16* scale, const bf16* shift, bf16* y,
                                                unsigned rows, unsigned cols, unsigned x_stride, unsigned y_stride,
                                                float eps, unsigned modulated) {
+  AGI_TRACE_KERNEL(1);
   __shared__ float scratch[32];
   grid_dependency_wait();
   const unsigned row = blockIdx.x;

@@ -271,6 +271,10 @@ Status Session::Prepare() {
     functions_.push_back(resolved[slot].second);
   }
   for (std::size_t slot = 0; slot < resolved.size(); ++slot) {
+    // Ask for the same (largest) shared-memory carve-out for every kernel of the recipe: consecutive launches
+    // then never make an SM wait to be re-partitioned between L1 and shared memory.  A hint; failure is ignored.
+    cu_->cuFuncSetAttribute(resolved[slot].second, CU_FUNC_ATTRIBUTE_PREFERRED_SHARED_MEMORY_CARVEOUT,
+                            CU_SHAREDMEM_CARVEOUT_MAX_SHARED);
     // Static and dynamic shared memory together may not pass 48 KB without the opt-in attribute.
     int static_bytes = 0;
     cu_->cuFuncGetAttribute(&static_bytes, CU_FUNC_ATTRIBUTE_SHARED_SIZE_BYTES, resolved[slot].second);

@@ -28,7 +28,7 @@ STATUS_WORD = 0          # u32: first error recorded by a kernel (0 = none)
 SM_COUNT = 148
 
 FLAG_BIAS, FLAG_RESIDUAL, FLAG_OUT_F32, FLAG_SCALED = 1, 2, 1 << 8, 1 << 9
-FLAG_LAYERNORM, FLAG_LN_MODULATE = 1 << 10, 1 << 11
+FLAG_LAYERNORM, FLAG_LN_MODULATE, FLAG_SLAB = 1 << 10, 1 << 11, 1 << 12
 ACT = {None: 0, "gelu_tanh": 1 << 4, "silu": 2 << 4, "relu": 3 << 4}
 PLAN_DTYPE_BYTES = {"F32": 4, "F16": 2, "BF16": 2, "F8_E4M3": 1, "I32": 4}
 
@@ -79,8 +79,11 @@ TC_SCRATCH_BYTES = 32 << 20    # fp32 partial tiles of split-K tensor-core GEMMs
 TC_COUNTER_BYTES = 16 << 10    # per-tile arrival counters of the same
 TC_SMEM_BUDGET = 200 * 1024    # dynamic shared memory a tensor-core GEMM CTA may use
 ATTN_SMEM_BUDGET = 200 * 1024    # dynamic shared memory of the keys-in-shared-memory attention kernel
-STREAM_SM_BYTES = 208 * 1024     # shared memory the bulk-stream GEMM CTAs of one SM may use together
-STREAM_CTA_BYTES = 104 * 1024    # and the most a single CTA takes (two CTAs per SM keep one draining while one fills)
+# One bulk copy per operand into unpadded rows was measured slower than one copy per row into padded rows:
+# unpadded rows make every fragment read an 8-way bank conflict and shared-memory reads bound the MMA phase.
+USE_SLAB_COPIES = False
+STREAM_SM_BYTES = 220 * 1024     # shared memory the bulk-stream GEMM CTAs of one SM may use together
+STREAM_CTA_BYTES = 110 * 1024    # and the most a single CTA takes (two CTAs per SM keep one draining while one fills)
 
 
 def tc_tiling(M: int, N: int, K: int, elem: int, splits: int | None = None) -> dict[str, int]:
@@ -101,7 +104,31 @@ def tc_tiling(M: int, N: int, K: int, elem: int, splits: int | None = None) -> d
             "shared_bytes": stages * stage_bytes + 1024}
 
 
-def stream_tiling(M: int, N: int, K: int, elem: int, extra_rows: int = 0) -> dict[str, int]:
+TC_CLUSTER_SIZES = {"bf16": (2, 3, 4, 6, 8), "e4m3": (2, 4, 8)}   # compiled cluster variants
+
+
+def tc_cluster_tiling(M: int, N: int, K: int, elem: int, dtype: str = "bf16") -> dict[str, int] | None:
+    """Geometry of ``agi_gemm_tc_*_c{C}``: the largest compiled cluster size that keeps all CTAs in one wave
+    (n_tiles * C <= 148) and leaves every slice at least two K blocks."""
+    if M > 64 or (K * elem) % 128:
+        return None
+    TN = ceil_div(M, 16) * 16
+    n_tiles = ceil_div(N, 128)
+    k_blocks = K * elem // 128
+    usable = [c for c in TC_CLUSTER_SIZES[dtype] if n_tiles * c <= SM_COUNT and k_blocks >= 2 * c]
+    if not usable:
+        return None
+    cluster = max(usable)
+    per = ceil_div(k_blocks, cluster)
+    if ceil_div(k_blocks, per) != cluster:      # every rank of the cluster must own a non-empty slice
+        return None
+    stage_bytes = 16384 + TN * 128
+    stages = max(3, min(12, TC_SMEM_BUDGET // stage_bytes, per))
+    return {"TN": TN, "n_tiles": n_tiles, "cluster": cluster, "stages": stages,
+            "shared_bytes": stages * stage_bytes + 1024 + cluster * ceil_div(TN, cluster) * 512}
+
+
+def stream_tiling(M: int, N: int, K: int, elem: int, extra_rows: int = 0, contiguous: bool = True) -> dict[str, int]:
     """Launch geometry of ``agi_gemm_stream_*``: rows per CTA, K windows per ring slot, slots.
 
     Aim: at least one CTA per SM when N allows it, every CTA resident at once (one wave), and the shared
@@ -111,17 +138,24 @@ def stream_tiling(M: int, N: int, K: int, elem: int, extra_rows: int = 0) -> dic
     rows = 16 if ceil_div(N, 16) >= SM_COUNT else 8
     grid = ceil_div(N, rows)
     per_sm = ceil_div(grid, SM_COUNT)
-    budget = min(STREAM_CTA_BYTES, STREAM_SM_BYTES // per_sm)
+    tiles = next(v for v in (1, 2, 3, 4, 6, 8) if 8 * v >= M)
+    warps = 4                                           # consumer warps (plus one producer warp)
+    tail = 16 + warps * 16 * (M | 1) * 4                # alignment slack + the warps' partial tiles
+    budget = min(STREAM_CTA_BYTES, STREAM_SM_BYTES // per_sm) - tail
     windows = K * elem // 64
     row_bytes = lambda w: w * 64 + 16
-    held = rows + M + extra_rows   # rows of a ring slot: weights, activations, optional AdaLN vectors
+    held = rows + M + extra_rows   # rows of a ring slot: weights, activations
+    common = {"rows": rows, "grid": grid, "tiles": tiles, "threads": (warps + 1) * 32}
+    if USE_SLAB_COPIES and contiguous and held * windows * 64 <= budget:
+        # whole K in one slot: unpadded rows, one bulk copy per operand ("slab" mode)
+        return {**common, "chunk_windows": windows, "slots": 1, "slab": True, "shared_bytes": held * windows * 64 + tail}
     if held * row_bytes(windows) <= budget:
         chunk_windows, slots = windows, 1
     else:
         chunk_windows = max(1, (budget // 2 // held - 16) // 64)
         slots = 2
-    return {"rows": rows, "grid": grid, "chunk_windows": chunk_windows, "slots": slots,
-            "shared_bytes": slots * held * row_bytes(chunk_windows)}
+    return {**common, "chunk_windows": chunk_windows, "slots": slots, "slab": False,
+            "shared_bytes": slots * held * row_bytes(chunk_windows) + tail}
 
 
 def grid_for(work_items: int, threads: int = 256, cap: int = SM_COUNT * 8) -> int:
@@ -318,13 +352,14 @@ class RecipeBuilder:
             # both operands reach shared memory by bulk copies; K is cut into chunks of <= ~100 KB per slot
             if M > 64 or (K * elem) % 64 or not aligned:
                 raise ValueError("stream GEMM needs M <= 64, K bytes % 64 == 0 and 16-byte aligned rows")
-            t = stream_tiling(M, N, K, elem)
-            rows, chunk_windows, slots = t["rows"], t["chunk_windows"], t["slots"]
-            tiles = next(t for t in (1, 2, 3, 4, 6, 8) if 8 * t >= M)
-            self.launch(f"agi_gemm_stream_{dtype}_t{tiles}", (ceil_div(N, rows), 1, 1), (160, 1, 1),
+            t = stream_tiling(M, N, K, elem, contiguous=(ldx or K) == K)
+            rows, chunk_windows, tiles = t["rows"], t["chunk_windows"], t["tiles"]
+            if t["slab"]:
+                args = args[:12] + [U32(flags | FLAG_SLAB)]
+            self.launch(f"agi_gemm_stream_{dtype}_t{tiles}", (ceil_div(N, rows), 1, 1), (t["threads"], 1, 1),
                         args[:7] + [Arena(STATUS_WORD)] + args[7:] + [U32(rows), U32(chunk_windows)],
-                        shared_bytes=slots * (rows + M) * (chunk_windows * 64 + 16),
-                        op=f"gemm_{dtype}", algorithm=f"bulk_stream_r{rows}_t{tiles}_c{chunk_windows}")
+                        shared_bytes=t["shared_bytes"], op=f"gemm_{dtype}",
+                        algorithm=f"bulk_stream_r{rows}_t{tiles}_c{chunk_windows}" + ("_slab" if t["slab"] else ""))
             return
         if tactic == "skinny":
             if M > 64 or (K * elem) % 64 or not aligned:
@@ -337,6 +372,17 @@ class RecipeBuilder:
         if tactic == "simt":
             self.launch(f"agi_gemm_simt_{dtype}", (ceil_div(N, 64), ceil_div(M, 64), 1), (256, 1, 1), args,
                         op=f"gemm_{dtype}", algorithm="simt_64x64x16")
+            return
+        if tactic == "cluster":
+            # tcgen05 with the K slices of a tile forming a thread-block cluster; partial sums meet in
+            # distributed shared memory (no global scratch, no atomics)
+            t = tc_cluster_tiling(M, N, K, elem, dtype)
+            if t is None:
+                raise ValueError("cluster split-K needs M <= 64, whole 128-byte K blocks and a usable cluster size")
+            self.launch(f"agi_gemm_tc_{dtype}_c{t['cluster']}", (t["n_tiles"], 1, t["cluster"]), (160, 1, 1),
+                        args[:7] + [dummy, dummy, Arena(STATUS_WORD)] + args[7:] + [U32(t["TN"]), U32(t["stages"])],
+                        shared_bytes=t["shared_bytes"], op=f"gemm_{dtype}",
+                        algorithm=f"tcgen05_128x{t['TN']}_s{t['stages']}_cluster{t['cluster']}")
             return
         if tactic != "tcgen05":
             raise ValueError(f"unknown GEMM tactic {tactic!r}")
@@ -352,24 +398,44 @@ class RecipeBuilder:
                     shared_bytes=t["shared_bytes"], op=f"gemm_{dtype}",
                     algorithm=f"tcgen05_128x{t['TN']}_s{t['stages']}_k{t['splits']}")
 
+    def gemm_batch(self, x: Pointer, parts: Sequence[tuple[Pointer, Pointer]], y: Pointer, M: int, N: int, K: int,
+                   seg_stride: int, ldx: int | None = None) -> None:
+        """Up to 16 bf16 GEMMs ``y[s] = x . W_s^T + b_s`` over the same ``x`` in one tensor-core launch;
+        ``y[s]`` starts ``seg_stride`` elements after ``y[s - 1]``."""
+        assert 1 <= len(parts) <= 16 and (K * 2) % 128 == 0
+        t = tc_tiling(M, N, K, 2, 1)
+        dummy = Arena(0)
+        ws = [p[0] for p in parts] + [dummy] * (16 - len(parts))
+        bs = [p[1] for p in parts] + [dummy] * (16 - len(parts))
+        self.launch("agi_gemm_tc_bf16_x16", (len(parts) * t["n_tiles"], t["m_tiles"], 1), (160, 1, 1),
+                    [x, y, Arena(STATUS_WORD), U32(M), U32(N), U32(K), U32(ldx or K), U32(N), U32(FLAG_BIAS), U32(t["TN"]),
+                     U32(t["stages"]), U32(seg_stride), *ws, *bs], shared_bytes=t["shared_bytes"], op="gemm_bf16_batch",
+                    algorithm=f"tcgen05_128x{t['TN']}_s{t['stages']}_x{len(parts)}")
+
     def fused_linear(self, x: Pointer, parts: Sequence[tuple[Pointer, Pointer | None, int]], y: Pointer, M: int, K: int,
                      *, ln: dict[str, Any] | None = None, ln_scratch: Pointer | None = None,
                      residual: Pointer | None = None, act: str | None = None, ldx: int | None = None,
-                     ldy: int | None = None, fuse: bool = True) -> None:
+                     ldy: int | None = None, fuse: bool = True, fuse_ln: bool = False) -> None:
         """``y[:, blocks] = epilogue(LN?(x) . [W0 | W1 | W2]^T)`` for bf16 and M <= 64.
 
         ``parts``: up to three ``(weight, bias or None, N_i)``; outputs land in consecutive column blocks of
         ``y``.  ``ln``: ``{"eps": e}`` for LayerNorm without affine, plus ``"scale"``/``"shift"`` pointers for
-        AdaLN modulation.  One launch of the fused bulk-stream kernel when the whole K range of a CTA fits one
-        ring slot; otherwise (or with ``fuse=False``) the same arithmetic as separate launches, normalising into
-        ``ln_scratch`` first."""
+        AdaLN modulation.  The weight matrices share one launch of the fused bulk-stream kernel.  The LayerNorm
+        is a launch of its own (into ``ln_scratch``) unless ``fuse_ln`` is set and the whole K range of a CTA
+        fits one ring slot: measured inside the action-head recipe, the in-kernel prologue (every CTA
+        normalising all rows again) costs more than the 2.8 us of the separate kernel.  ``fuse=False`` gives
+        one launch per weight matrix."""
         total = sum(n for _, _, n in parts)
         ldy = ldy or total
-        t = stream_tiling(M, total, K, 2)
+        t = stream_tiling(M, total, K, 2, contiguous=(ldx or K) == K)
         rows = t["rows"]
         fits = (M <= 64 and (K * 2) % 64 == 0 and len(parts) <= 3 and all(n % rows == 0 for _, _, n in parts)
-                and (ln is None or (t["slots"] == 1 and ("scale" not in ln or K <= 1536)))
+                and (ln is None or (t["slots"] == 1 and K <= 1536))
                 and len({b is None for _, b, _ in parts}) == 1)
+        if fuse and fits and ln is not None and not fuse_ln:
+            assert ln_scratch is not None, "a separate LayerNorm needs a buffer for the normalised activations"
+            self.layernorm(x, ln_scratch, M, K, ln["eps"], scale=ln.get("scale"), shift=ln.get("shift"), x_stride=ldx)
+            x, ldx, ln = ln_scratch, None, None
         if not (fuse and fits):
             src = x
             if ln is not None:
@@ -386,12 +452,15 @@ class RecipeBuilder:
         flags = ACT[act] | (FLAG_BIAS if parts[0][1] is not None else 0) | (FLAG_RESIDUAL if residual else 0)
         if ln is not None:
             flags |= FLAG_LAYERNORM | (FLAG_LN_MODULATE if "scale" in ln else 0)
+        if t["slab"]:
+            flags |= FLAG_SLAB
         dummy = Arena(0)
         ws = [p[0] for p in parts] + [dummy] * (3 - len(parts))
         bs = [(p[1] or dummy) for p in parts] + [dummy] * (3 - len(parts))
         ns = [p[2] for p in parts] + [0] * (3 - len(parts))
-        tiles = next(v for v in (1, 2, 3, 4, 6, 8) if 8 * v >= M)
-        self.launch(f"agi_gemm_stream_fused_bf16_t{tiles}", (t["grid"], 1, 1), (160, 1, 1),
+        tiles = t["tiles"]
+        family = "lnfused" if ln is not None else "fused"
+        self.launch(f"agi_gemm_stream_{family}_bf16_t{tiles}", (t["grid"], 1, 1), (t["threads"], 1, 1),
                     [x, *ws, y, *bs, residual or dummy, (ln or {}).get("scale", dummy), (ln or {}).get("shift", dummy),
                      Arena(STATUS_WORD), U32(M), *map(U32, ns), U32(K), U32(ldx or K), U32(ldy), U32(flags), U32(rows),
                      U32(t["chunk_windows"]), F32((ln or {}).get("eps", 0.0))],

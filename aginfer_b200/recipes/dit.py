@@ -113,7 +113,7 @@ def synthetic_inputs(cfg: DitConfig, seed: int = 2) -> dict:
 
 def build_recipe(cfg: DitConfig = DitConfig(), weights: Mapping[str, tuple[str, tuple[int, ...]]] | None = None,
                  gemm_tactic: str = "auto", profile: str = "default", stream_profile: bool = False,
-                 fuse: bool = True) -> RecipeBuilder:
+                 fuse: bool = True, batch_kv: bool = True) -> RecipeBuilder:
     D, T, H, S = cfg.hidden, cfg.tokens, cfg.horizon, cfg.steps
     r = RecipeBuilder(weights or {k: ("BF16", v) for k, v in weight_shapes(cfg).items()})
     r.begin_profile(profile, [io("backbone_features", "BF16", [cfg.backbone_tokens, cfg.backbone_dim]),
@@ -134,18 +134,28 @@ def build_recipe(cfg: DitConfig = DitConfig(), weights: Mapping[str, tuple[str, 
     seq = r.alloc(T * D * BF)                        # residual stream [state token; action tokens]
     state_tok = r.alloc(D * BF)
     mods = [r.alloc(S * 2 * D * BF) for _ in range(cfg.layers + 1)]   # AdaLN (scale | shift) per step
-    kv = {l: (r.alloc(cfg.backbone_tokens * D * BF), r.alloc(cfg.backbone_tokens * D * BF))
-          for l in range(cfg.layers) if cfg.is_cross(l)}
+    cross = [l for l in range(cfg.layers) if cfg.is_cross(l)]
+    kv_bytes = cfg.backbone_tokens * D * BF
+    kv_all = r.alloc(2 * len(cross) * kv_bytes)      # K then V of every cross-attention block, back to back
+    kv = {l: (kv_all + 2 * i * kv_bytes, kv_all + (2 * i + 1) * kv_bytes) for i, l in enumerate(cross)}
 
     # ---- once per chunk --------------------------------------------------------------------
     mark = r.mark()
     h_state = r.alloc(cfg.encoder_hidden * BF)
     lin(Tensor("state"), f"{P}.state_encoder.fc1", h_state, 1, cfg.encoder_hidden, cfg.state_dim, act="relu")
     lin(h_state, f"{P}.state_encoder.fc2", state_tok, 1, D, cfg.encoder_hidden)
-    for l, (k_buf, v_buf) in kv.items():
-        b = f"{P}.dit.blocks.{l}.attn"
-        lin(Tensor("backbone_features"), f"{b}.to_k", k_buf, cfg.backbone_tokens, D, cfg.backbone_dim)
-        lin(Tensor("backbone_features"), f"{b}.to_v", v_buf, cfg.backbone_tokens, D, cfg.backbone_dim)
+    if batch_kv and (cfg.backbone_dim * BF) % 128 == 0:
+        # every block's K and V projection of the context tokens, 16 at a time, as one tensor-core launch
+        jobs = [(Weight(f"{P}.dit.blocks.{l}.attn.{n}.weight"), Weight(f"{P}.dit.blocks.{l}.attn.{n}.bias"))
+                for l in cross for n in ("to_k", "to_v")]
+        for i in range(0, len(jobs), 16):
+            r.gemm_batch(Tensor("backbone_features"), jobs[i:i + 16], kv_all + i * kv_bytes, cfg.backbone_tokens, D,
+                         cfg.backbone_dim, seg_stride=cfg.backbone_tokens * D)
+    else:
+        for l, (k_buf, v_buf) in kv.items():
+            b = f"{P}.dit.blocks.{l}.attn"
+            lin(Tensor("backbone_features"), f"{b}.to_k", k_buf, cfg.backbone_tokens, D, cfg.backbone_dim)
+            lin(Tensor("backbone_features"), f"{b}.to_v", v_buf, cfg.backbone_tokens, D, cfg.backbone_dim)
     t_sin, t_hid, temb, temb_act = (r.alloc(S * cfg.time_dim * BF), r.alloc(S * D * BF), r.alloc(S * D * BF),
                                     r.alloc(S * D * BF))
     times = cfg.step_times()

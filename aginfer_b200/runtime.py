@@ -174,11 +174,15 @@ class Runtime:
         return {name: getattr(out, name) for name, _ in _RuntimeOptions._fields_}
 
     def close(self) -> None:
-        if self._h:
-            load_library().agi_runtime_destroy(self._h)
-            self._h = None
+        if self._h and _lib is not None:   # at interpreter shutdown the module may already be torn down
+            _lib.agi_runtime_destroy(self._h)
+        self._h = None
 
-    __del__ = close
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 class Model:
@@ -202,11 +206,15 @@ class Model:
         return found
 
     def close(self) -> None:
-        if self._h:
-            load_library().agi_model_destroy(self._h)
-            self._h = None
+        if self._h and _lib is not None:   # at interpreter shutdown the module may already be torn down
+            _lib.agi_model_destroy(self._h)
+        self._h = None
 
-    __del__ = close
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 class Session:
@@ -266,11 +274,15 @@ class Session:
         return {name: getattr(out, name) for name, _ in _Stats._fields_}
 
     def close(self) -> None:
-        if self._h:
-            load_library().agi_session_destroy(self._h)
-            self._h = None
+        if self._h and _lib is not None:   # at interpreter shutdown the module may already be torn down
+            _lib.agi_session_destroy(self._h)
+        self._h = None
 
-    __del__ = close
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 def sha256(data: bytes, portable: bool = False) -> bytes:

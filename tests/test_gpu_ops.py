@@ -304,14 +304,47 @@ def test_fused_layernorm_qkv_linear(tmp_path, fuse, modulated):
         ln = {"eps": 1e-5}
         if modulated:
             ln |= {"scale": Weight("mod"), "shift": Weight("mod") + 2 * K}
-        r.fused_linear(Tensor("x"), [(Weight(f"w{i}"), Weight(f"b{i}"), N) for i in range(3)], Tensor("y"), M, K,
-                       ln=ln, ln_scratch=scratch, fuse=fuse)
+        out = r.alloc(M * 3 * N * 2)   # column blocks need pointer arithmetic, which caller tensors do not allow
+        r.fused_linear(Tensor("x"), [(Weight(f"w{i}"), Weight(f"b{i}"), N) for i in range(3)], out, M, K,
+                       ln=ln, ln_scratch=scratch, fuse=fuse, fuse_ln=True)
+        from aginfer_b200.recipes import U32
+        r.launch("agi_copy_rows_bf16", (296, 1, 1), (256, 1, 1), [out, Tensor("y"), U32(M), U32(3 * N), U32(3 * N), U32(3 * N)])
         r.export_status(Tensor("status"))
 
     got, stats = run_recipe(tmp_path, weights, {"x": x}, {"y": (BF, (M, 3 * N)), "status": (torch.int32, (1,))}, body,
                             repeats=2)
     assert got["status"].item() == 0
-    assert stats["launches_per_enqueue"] == (3 if fuse else 6)
+    assert stats["launches_per_enqueue"] == (4 if fuse else 7)
     h = ops.layernorm(x, 1e-5, mod[:K], mod[K:]) if modulated else ops.layernorm(x, 1e-5)
     want = torch.cat([ops.gemm(h, ws[i], bias=bs[i]) for i in range(3)], dim=1)
     assert ops.max_rel_err(got["y"], want) < 1e-2
+
+
+CLUSTER_CASES = [(17, 1536, 1536, "bias_gelu_res"), (17, 6144, 1536, "bias_gelu"), (17, 1536, 6144, "bias_res"),
+                 (17, 4608, 1536, "bias"), (4, 3072, 1536, "bias"), (50, 1024, 4096, "plain"), (1, 2048, 2048, "plain"),
+                 (33, 1000, 1024, "bias")]
+
+
+@pytest.mark.parametrize("case", CLUSTER_CASES, ids=lambda c: "-".join(map(str, c)))
+def test_gemm_tcgen05_cluster_split_k(tmp_path, case):
+    from aginfer_b200.recipes.builder import tc_cluster_tiling
+    M, N, K, epi = case
+    assert tc_cluster_tiling(M, N, K, 2) is not None
+    x, w = randn(M, K, seed=51), randn(N, K, seed=52, std=0.02)
+    bias = randn(N, seed=53, std=0.1) if "bias" in epi else None
+    res = randn(M, N, seed=54) if "res" in epi else None
+    act = "gelu_tanh" if "gelu" in epi else None
+    weights, inputs = {"w": w}, {"x": x}
+    if bias is not None:
+        weights["b"] = bias
+    if res is not None:
+        inputs["res"] = res
+
+    def body(r):
+        r.gemm(Tensor("x"), Weight("w"), Tensor("y"), M, N, K, bias=Weight("b") if bias is not None else None,
+               residual=Tensor("res") if res is not None else None, act=act, tactic="cluster")
+        r.export_status(Tensor("status"))
+
+    got, _ = run_recipe(tmp_path, weights, inputs, {"y": (BF, (M, N)), "status": (torch.int32, (1,))}, body, repeats=3)
+    assert got["status"].item() == 0, hex(got["status"].item())
+    assert ops.max_rel_err(got["y"], ops.gemm(x, w, bias=bias, residual=res, act=act)) < 1e-2
