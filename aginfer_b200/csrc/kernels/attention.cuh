@@ -6,6 +6,15 @@
 
 #include "common.cuh"
 
+// m16n8k16 bf16 MMA with fp32 accumulation (D = A.B + D).
+__device__ __forceinline__ void skinny_mma_bf16(float c[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
+                                                unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
 constexpr int kAttnWarps = 8;
 constexpr int kAttnChunk = 32;
 constexpr int kAttnMaxDim = 128;
@@ -237,5 +246,335 @@ agi_attention_smem_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, un
     }
     const float ox = (acc[0].x + acc[1].x) + (acc[2].x + acc[3].x), oy = (acc[0].y + acc[1].y) + (acc[2].y + acc[3].y);
     *reinterpret_cast<bf162*>(o + size_t(row) * o_stride + head * head_dim + d) = __floats2bfloat162_rn(ox * inv, oy * inv);
+  }
+}
+
+// Attention for a handful of query rows (the action head: 17 queries against 17 or 300 keys).  One block
+// per head.  The head's K and V rows are fetched once; the 8 warps split the KEYS (flash-decoding style),
+// each computing scores, a local softmax and a partial P.V for all query rows over its own key range; the
+// partial results are merged through shared memory with the usual max/sum rescaling.  Latency, not
+// throughput, decides this kernel: every phase is a short loop over registers and shared memory.
+// grid = (q_heads), block = 256; q_rows <= 32, head_dim <= 64 and a multiple of 8.
+// dynamic shared memory: see attention_rows_smem_bytes in the recipe builder.
+constexpr int kRowsMax = 32;
+
+extern "C" __global__ void __launch_bounds__(kAttnWarps * 32)
+agi_attention_rows_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, unsigned q_rows, unsigned kv_rows,
+                        unsigned q_heads, unsigned kv_heads, unsigned head_dim, unsigned q_stride, unsigned k_stride,
+                        unsigned v_stride, unsigned o_stride, float scale, unsigned mask_mode, unsigned mask_arg) {
+  AGI_TRACE_KERNEL(9);
+  extern __shared__ __align__(16) unsigned char attn_smem[];
+  grid_dependency_wait();
+  const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const unsigned head = blockIdx.x, kv_head = head / (q_heads / kv_heads);
+  const unsigned k_pitch = head_dim + 2, kv_pad = (kv_rows + 31) & ~31u;
+  bf16* k_tile = reinterpret_cast<bf16*>(attn_smem);
+  bf16* v_tile = k_tile + ((size_t(kv_rows) * k_pitch + 7) & ~size_t(7));
+  float* q_tile = reinterpret_cast<float*>(v_tile + size_t(kv_rows) * head_dim);   // [rows][head_dim]
+  float* p_tile = q_tile + q_rows * head_dim;                                       // [rows][kv_pad]
+  float* o_part = p_tile + q_rows * kv_pad;                                         // [warps][rows][head_dim]
+  float* m_part = o_part + kAttnWarps * q_rows * head_dim;                          // [warps][rows]
+  float* l_part = m_part + kAttnWarps * q_rows;
+
+  // ---- stage K, V (batches of independent 16-byte loads) and Q (pre-scaled) ----
+  const unsigned vec_per_row = head_dim / 8, vectors = kv_rows * vec_per_row;
+  constexpr int kBatch = 4;
+  for (unsigned i0 = threadIdx.x; i0 < vectors; i0 += kBatch * blockDim.x) {
+    uint4 kk[kBatch], vv[kBatch];
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b) {
+      const unsigned i = i0 + b * blockDim.x;
+      if (i < vectors) {
+        const size_t key = i / vec_per_row;
+        const unsigned d = (i % vec_per_row) * 8;
+        kk[b] = __ldg(reinterpret_cast<const uint4*>(k + key * k_stride + kv_head * head_dim + d));
+        vv[b] = __ldg(reinterpret_cast<const uint4*>(v + key * v_stride + kv_head * head_dim + d));
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b) {
+      const unsigned i = i0 + b * blockDim.x;
+      if (i < vectors) {
+        const unsigned j = i / vec_per_row, d = (i % vec_per_row) * 8;
+        unsigned* kd = reinterpret_cast<unsigned*>(&k_tile[j * k_pitch + d]);
+        kd[0] = kk[b].x; kd[1] = kk[b].y; kd[2] = kk[b].z; kd[3] = kk[b].w;
+        *reinterpret_cast<uint4*>(&v_tile[j * head_dim + d]) = vv[b];
+      }
+    }
+  }
+  for (unsigned i = threadIdx.x; i < q_rows * head_dim; i += blockDim.x) {
+    const unsigned r = i / head_dim, d = i % head_dim;
+    q_tile[i] = __bfloat162float(q[size_t(r) * q_stride + head * head_dim + d]) * scale;
+  }
+  __syncthreads();
+
+  // ---- this warp's key range ----
+  const unsigned per_warp = (kv_rows + kAttnWarps - 1) / kAttnWarps;
+  const unsigned key_lo = min(warp * per_warp, kv_rows), key_hi = min(key_lo + per_warp, kv_rows);
+
+  // scores: a lane keeps one key row in registers and visits every query row
+  for (unsigned key = key_lo + lane; key < key_hi; key += 32) {
+    bf162 kr[32];  // head_dim / 2 <= 32 pairs
+#pragma unroll
+    for (int d2 = 0; d2 < 32; ++d2)
+      if (2 * d2 < head_dim) kr[d2] = *reinterpret_cast<const bf162*>(k_tile + key * k_pitch + 2 * d2);
+    for (unsigned r = 0; r < q_rows; ++r) {
+      const float2* qr = reinterpret_cast<const float2*>(q_tile + r * head_dim);
+      float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+      for (int d2 = 0; d2 < 32; ++d2)
+        if (2 * d2 < head_dim) {
+          const float2 kk = __bfloat1622float2(kr[d2]);
+          const float2 qq = qr[d2];
+          s0 += qq.x * kk.x;
+          s1 += qq.y * kk.y;
+        }
+      bool visible = true;
+      if (mask_mode == 1) visible = key <= r + mask_arg;
+      if (mask_mode == 2) visible = key / mask_arg == r / mask_arg;
+      p_tile[r * kv_pad + key] = visible ? s0 + s1 : -3.0e38f;
+    }
+  }
+  __syncwarp();
+  // local softmax over this warp's keys, row by row
+  for (unsigned r = 0; r < q_rows; ++r) {
+    float best = -3.0e38f;
+    for (unsigned key = key_lo + lane; key < key_hi; key += 32) best = fmaxf(best, p_tile[r * kv_pad + key]);
+    best = warp_max(best);
+    float sum = 0.f;
+    for (unsigned key = key_lo + lane; key < key_hi; key += 32) {
+      const float s = p_tile[r * kv_pad + key];
+      const float e = s > -1.0e38f ? __expf(s - best) : 0.f;
+      p_tile[r * kv_pad + key] = e;
+      sum += e;
+    }
+    sum = warp_sum(sum);
+    if (lane == 0) {
+      m_part[warp * q_rows + r] = best;
+      l_part[warp * q_rows + r] = sum;
+    }
+  }
+  __syncwarp();
+  // partial P.V: a lane owns one pair of output dimensions for every query row
+  if (2 * lane < head_dim) {
+    float2 acc[kRowsMax];
+#pragma unroll
+    for (int r = 0; r < kRowsMax; ++r) acc[r] = make_float2(0.f, 0.f);
+    for (unsigned key = key_lo; key < key_hi; ++key) {
+      const float2 vv = __bfloat1622float2(*reinterpret_cast<const bf162*>(v_tile + key * head_dim + 2 * lane));
+#pragma unroll
+      for (int r = 0; r < kRowsMax; ++r)
+        if (r < q_rows) {
+          const float pj = p_tile[r * kv_pad + key];
+          acc[r].x += pj * vv.x;
+          acc[r].y += pj * vv.y;
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < kRowsMax; ++r)
+      if (r < q_rows) *reinterpret_cast<float2*>(o_part + (warp * q_rows + r) * head_dim + 2 * lane) = acc[r];
+  }
+  __syncthreads();
+  // merge the 8 partial results
+  for (unsigned i = threadIdx.x; i < q_rows * head_dim; i += blockDim.x) {
+    const unsigned r = i / head_dim, d = i % head_dim;
+    float best = -3.0e38f;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) best = fmaxf(best, m_part[w * q_rows + r]);
+    float num = 0.f, den = 0.f;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) {
+      const float mw = m_part[w * q_rows + r];
+      const float f = mw > -1.0e38f ? __expf(mw - best) : 0.f;
+      num += f * o_part[(w * q_rows + r) * head_dim + d];
+      den += f * l_part[w * q_rows + r];
+    }
+    o[size_t(r) * o_stride + head * head_dim + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+  }
+}
+
+// Tensor-core attention for a handful of query rows (the action head: 17 queries, 17 or 300 keys,
+// head_dim 48).  One block of 4 warps per head.  K is staged row-major and V transposed in shared memory so
+// that both are MMA "B" operands with contiguous pairs; Q stays in registers as the "A" operand.  Each warp
+// takes every fourth pair of 8-key tiles and runs the usual streaming softmax on the m16n8k16 accumulators
+// (scores -> running max / sum per row -> P re-used directly as the A operand of P.V); the four warps'
+// (max, sum, O) are merged through shared memory at the end.  About 25 MMAs per 16 keys instead of
+// thousands of scalar instructions: the kernel is latency-bound, so instruction count is what matters.
+// grid = (q_heads), block = 128; q_rows <= 32; head_dim a multiple of 16, <= 64.
+// dynamic shared memory = kv16 * (head_dim + 2) * 2 (K) + head_dim * (kv16 + 2) * 2 (V^T) + merge area
+//   4 * 32 * (head_dim + 2) * 4, kv16 = kv_rows rounded up to 16.
+extern "C" __global__ void __launch_bounds__(128)
+agi_attention_mma_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, unsigned q_rows, unsigned kv_rows,
+                       unsigned q_heads, unsigned kv_heads, unsigned head_dim, unsigned q_stride, unsigned k_stride,
+                       unsigned v_stride, unsigned o_stride, float scale, unsigned mask_mode, unsigned mask_arg) {
+  AGI_TRACE_KERNEL(10);
+  extern __shared__ __align__(16) unsigned char attn_smem[];
+  grid_dependency_wait();
+  const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+  const unsigned head = blockIdx.x, kv_head = head / (q_heads / kv_heads);
+  const unsigned kv16 = (kv_rows + 15) & ~15u;
+  const unsigned k_pitch = head_dim + 2;   // elements; odd word count: the 8 key rows of a fragment hit 8 banks
+  const unsigned vt_pitch = kv16 + 2;
+  bf16* k_tile = reinterpret_cast<bf16*>(attn_smem);               // [kv16][k_pitch]
+  bf16* vt_tile = k_tile + size_t(kv16) * k_pitch;                 // [head_dim][vt_pitch]  (V transposed)
+  float* merge = reinterpret_cast<float*>(vt_tile + size_t(head_dim) * vt_pitch + ((size_t(head_dim) * vt_pitch) & 1));
+
+  // ---- stage K (row-major) and V (transposed); rows past kv_rows are zero ----
+  const unsigned vec_per_row = head_dim / 8;
+  for (unsigned i = threadIdx.x; i < kv16 * vec_per_row; i += blockDim.x) {
+    const unsigned j = i / vec_per_row, d = (i % vec_per_row) * 8;
+    uint4 kk = make_uint4(0, 0, 0, 0), vv = kk;
+    if (j < kv_rows) {
+      kk = __ldg(reinterpret_cast<const uint4*>(k + size_t(j) * k_stride + kv_head * head_dim + d));
+      vv = __ldg(reinterpret_cast<const uint4*>(v + size_t(j) * v_stride + kv_head * head_dim + d));
+    }
+    unsigned* kd = reinterpret_cast<unsigned*>(&k_tile[j * k_pitch + d]);
+    kd[0] = kk.x; kd[1] = kk.y; kd[2] = kk.z; kd[3] = kk.w;
+    const bf16* ve = reinterpret_cast<const bf16*>(&vv);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) vt_tile[(d + e) * vt_pitch + j] = ve[e];
+  }
+  // ---- Q fragments (A operand), pre-scaled: rows g, g + 8 of each 16-row tile; zero past q_rows ----
+  const unsigned ksteps = head_dim / 16;   // <= 4
+  unsigned qa[2][4][4];
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        qa[mt][ks][r] = 0;
+        const unsigned row = mt * 16 + g + (r & 1) * 8, col = ks * 16 + 2 * t + (r >> 1) * 8;
+        if (ks < ksteps && row < q_rows) {
+          const bf162 pair = *reinterpret_cast<const bf162*>(q + size_t(row) * q_stride + head * head_dim + col);
+          const float2 f = __bfloat1622float2(pair);
+          const bf162 scaled = __floats2bfloat162_rn(f.x * scale, f.y * scale);
+          qa[mt][ks][r] = *reinterpret_cast<const unsigned*>(&scaled);
+        }
+      }
+  __syncthreads();
+
+  // running softmax state of this thread's 4 rows (mt 0/1 x rows g, g + 8) and its output accumulators
+  float row_max[2][2], row_sum[2][2], out[2][8][4];
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt) {
+    row_max[mt][0] = row_max[mt][1] = -3.0e38f;
+    row_sum[mt][0] = row_sum[mt][1] = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) out[mt][nt][i] = 0.f;
+  }
+  const unsigned dtiles = head_dim / 8;    // <= 8
+  const unsigned m_tiles = q_rows > 16 ? 2 : 1;
+
+  for (unsigned key0 = warp * 16; key0 < kv16; key0 += 64) {   // this warp's 16-key blocks
+    // B fragments of K for the two 8-key tiles: b0 = (d 2t..2t+1, key g), b1 = (d 2t+8.., key g)
+    unsigned kb[2][4][2];
+#pragma unroll
+    for (int half = 0; half < 2; ++half)
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks)
+        if (ks < ksteps) {
+          const bf16* row = k_tile + (key0 + half * 8 + g) * k_pitch + ks * 16 + 2 * t;
+          kb[half][ks][0] = *reinterpret_cast<const unsigned*>(row);
+          kb[half][ks][1] = *reinterpret_cast<const unsigned*>(row + 8);
+        }
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) {
+      if (mt >= m_tiles) break;
+      float s[2][4];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        s[half][0] = s[half][1] = s[half][2] = s[half][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          if (ks < ksteps)
+            skinny_mma_bf16(s[half], qa[mt][ks][0], qa[mt][ks][1], qa[mt][ks][2], qa[mt][ks][3], kb[half][ks][0], kb[half][ks][1]);
+      }
+      // mask, then per-row maximum over these 16 keys (own 4 values, then across the quad)
+#pragma unroll
+      for (int half = 0; half < 2; ++half)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const unsigned key = key0 + half * 8 + 2 * t + (i & 1), row = mt * 16 + g + (i >> 1) * 8;
+          bool visible = key < kv_rows;
+          if (mask_mode == 1) visible = visible && key <= row + mask_arg;
+          if (mask_mode == 2) visible = visible && key / mask_arg == row / mask_arg;
+          if (!visible) s[half][i] = -3.0e38f;
+        }
+      unsigned pa[4];
+#pragma unroll
+      for (int hr = 0; hr < 2; ++hr) {  // hr 0: row g (c0,c1), hr 1: row g + 8 (c2,c3)
+        float tile_max = fmaxf(fmaxf(s[0][2 * hr], s[0][2 * hr + 1]), fmaxf(s[1][2 * hr], s[1][2 * hr + 1]));
+        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
+        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
+        const float new_max = fmaxf(row_max[mt][hr], tile_max);
+        const float rescale = new_max > -1.0e38f ? __expf(row_max[mt][hr] - new_max) : 1.f;
+        float p[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float sc = s[j >> 1][2 * hr + (j & 1)];
+          p[j] = sc > -1.0e38f ? __expf(sc - new_max) : 0.f;
+        }
+        float tile_sum = (p[0] + p[1]) + (p[2] + p[3]);
+        tile_sum += __shfl_xor_sync(0xffffffffu, tile_sum, 1);
+        tile_sum += __shfl_xor_sync(0xffffffffu, tile_sum, 2);
+        row_sum[mt][hr] = row_sum[mt][hr] * rescale + tile_sum;
+        row_max[mt][hr] = new_max;
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+          out[mt][nt][2 * hr] *= rescale;
+          out[mt][nt][2 * hr + 1] *= rescale;
+        }
+        // P as the A operand of P.V: a0/a1 = keys 2t..2t+1 (first tile), a2/a3 = keys 2t+8.. (second tile)
+        const bf162 lo = __floats2bfloat162_rn(p[0], p[1]), hi = __floats2bfloat162_rn(p[2], p[3]);
+        pa[hr] = *reinterpret_cast<const unsigned*>(&lo);
+        pa[2 + hr] = *reinterpret_cast<const unsigned*>(&hi);
+      }
+      // O += P (16 x 16 keys) . V (16 keys x 8 dims) per 8-dim tile; V^T rows give contiguous key pairs
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt)
+        if (nt < dtiles) {
+          const bf16* row = vt_tile + (nt * 8 + g) * vt_pitch + key0 + 2 * t;
+          const unsigned b0 = *reinterpret_cast<const unsigned*>(row), b1 = *reinterpret_cast<const unsigned*>(row + 8);
+          skinny_mma_bf16(out[mt][nt], pa[0], pa[1], pa[2], pa[3], b0, b1);
+        }
+    }
+  }
+
+  // ---- merge the four warps: [warp][row 0..31][head_dim + 2] with max and sum in the last two columns ----
+  const unsigned mp = head_dim + 2;
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int hr = 0; hr < 2; ++hr) {
+      float* dst = merge + (size_t(warp) * 32 + mt * 16 + g + hr * 8) * mp;
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt)
+        if (nt < dtiles) {
+          dst[nt * 8 + 2 * t] = out[mt][nt][2 * hr];
+          dst[nt * 8 + 2 * t + 1] = out[mt][nt][2 * hr + 1];
+        }
+      if (t == 0) {
+        dst[head_dim] = row_max[mt][hr];
+        dst[head_dim + 1] = row_sum[mt][hr];
+      }
+    }
+  __syncthreads();
+  for (unsigned i = threadIdx.x; i < q_rows * head_dim; i += blockDim.x) {
+    const unsigned r = i / head_dim, d = i % head_dim;
+    float best = -3.0e38f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) best = fmaxf(best, merge[(w * 32 + r) * mp + head_dim]);
+    float num = 0.f, den = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float* src = merge + (w * 32 + r) * mp;
+      const float f = src[head_dim] > -1.0e38f ? __expf(src[head_dim] - best) : 0.f;
+      num += f * src[d];
+      den += f * src[head_dim + 1];
+    }
+    o[size_t(r) * o_stride + head * head_dim + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
   }
 }

@@ -33,8 +33,13 @@ enum : unsigned {
 // serialization, a kernel may start while its predecessor drains; `grid_dependency_wait`
 // blocks until the predecessor's writes are visible.  Without that launch attribute both
 // instructions do nothing.
-__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// `grid_dependency_release` lets the successor's blocks be scheduled (they run their own prologue - barrier
+// set-up, weight prefetch - and then block in their own wait until this grid has completed and flushed).
 __device__ __forceinline__ void grid_dependency_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // release as early as possible, then wait
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
 
 // Launch timeline for tuning (-DAGI_TRACE only; compiled out of the shipped bundle): block (0,0,0) of every
 // kernel records the global timer when it starts and when it finishes.

@@ -312,6 +312,22 @@ class RecipeBuilder:
         span_pad = ceil_div(span, 32) * 32
         smem = span * (2 * head_dim + 2) * 2 + 16 + 8 * head_dim * 4 + 8 * span_pad * 4
         aligned = head_dim % 8 == 0 and k_stride % 8 == 0 and v_stride % 8 == 0
+        rows_smem = (ceil_div(kv_rows * (head_dim + 2), 8) * 16 + kv_rows * head_dim * 2 + q_rows * head_dim * 4
+                     + q_rows * ceil_div(kv_rows, 32) * 32 * 4 + 8 * q_rows * head_dim * 4 + 2 * 8 * q_rows * 4)
+        kv16 = ceil_div(kv_rows, 16) * 16
+        mma_smem = kv16 * (head_dim + 2) * 2 + head_dim * (kv16 + 2) * 2 + 8 + 4 * 32 * (head_dim + 2) * 4
+        if (aligned and q_rows <= 32 and head_dim <= 64 and head_dim % 16 == 0 and q_stride % 2 == 0
+                and mma_smem <= ATTN_SMEM_BUDGET and algorithm in ("auto", "mma")):
+            # few query rows: one block per head, tensor-core scores and P.V
+            self.launch("agi_attention_mma_bf16", (q_heads, 1, 1), (128, 1, 1), args, shared_bytes=mma_smem,
+                        op=f"attention_{mask}", algorithm="mma_key_split")
+            return
+        if (aligned and q_rows <= 32 and head_dim <= 64 and rows_smem <= ATTN_SMEM_BUDGET
+                and algorithm in ("auto", "key_split")):
+            # few query rows: one block per head, warps split the keys
+            self.launch("agi_attention_rows_bf16", (q_heads, 1, 1), (256, 1, 1), args, shared_bytes=rows_smem,
+                        op=f"attention_{mask}", algorithm="key_split")
+            return
         if aligned and smem <= ATTN_SMEM_BUDGET and algorithm != "warp_per_row":
             self.launch("agi_attention_smem_bf16", (ceil_div(q_rows, 8), q_heads, 1), (256, 1, 1), args + [U32(span)],
                         shared_bytes=smem, op=f"attention_{mask}", algorithm="keys_in_smem")

@@ -31,7 +31,7 @@ def test_recipe_compiles_and_is_one_graph_safe_profile():
     per_step = [l for l in launches if l["kernel"] == "agi_euler_step"]
     assert len(per_step) == cfg.steps
     kernels = {l["kernel"] for l in launches}
-    assert {"agi_gemm_tc_bf16_x16", "agi_gemm_stream_bf16_t3", "agi_attention_smem_bf16", "agi_layernorm_bf16"} <= kernels
+    assert {"agi_gemm_tc_bf16_x16", "agi_gemm_stream_bf16_t3", "agi_attention_mma_bf16", "agi_layernorm_bf16"} <= kernels
     # every weight of the checkpoint is used by some launch
     used = {a["weights_offset"] for l in launches for a in l["arguments"] if "weights_offset" in a}
     assert used == set(r.weight_offsets.values())

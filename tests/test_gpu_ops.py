@@ -130,10 +130,12 @@ ATTENTION_CASES = [
     (512, 512, 16, 16, 80, "block", 256),     # vision full attention, per image
     (50, 306, 8, 4, 128, "causal", 256),      # action expert over [prefix | suffix]
     (5, 3, 2, 1, 16, "none", 0),              # ragged, smaller than one tile
+    (32, 77, 6, 3, 64, "causal", 45),         # few queries, GQA, causal with an offset
+    (20, 40, 4, 4, 32, "block", 10),          # few queries, block-diagonal
 ]
 
 
-@pytest.mark.parametrize("algorithm", ["warp_per_row", "auto"])
+@pytest.mark.parametrize("algorithm", ["warp_per_row", "keys_in_smem", "key_split", "auto"])
 @pytest.mark.parametrize("case", ATTENTION_CASES, ids=lambda c: "x".join(map(str, c)))
 def test_attention(tmp_path, case, algorithm):
     sq, skv, hq, hkv, d, mask, arg = case
