@@ -394,16 +394,16 @@ agi_attention_rows_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, un
 }
 
 // Tensor-core attention for a handful of query rows (the action head: 17 queries, 17 or 300 keys,
-// head_dim 48).  One block of 4 warps per head.  K is staged row-major and V transposed in shared memory so
-// that both are MMA "B" operands with contiguous pairs; Q stays in registers as the "A" operand.  Each warp
-// takes every fourth pair of 8-key tiles and runs the usual streaming softmax on the m16n8k16 accumulators
-// (scores -> running max / sum per row -> P re-used directly as the A operand of P.V); the four warps'
+// head_dim 48).  One block of 8 warps per (head, 16-row tile of queries).  K and V are staged row-major in shared memory (K rows are the
+// "B" operand of Q.K^T as they are, V goes through ldmatrix.trans for P.V); Q stays in registers as the "A" operand.  Each warp
+// takes every eighth pair of 8-key tiles and runs the usual streaming softmax on the m16n8k16 accumulators
+// (scores -> running max / sum per row -> P re-used directly as the A operand of P.V); the eight warps'
 // (max, sum, O) are merged through shared memory at the end.  About 25 MMAs per 16 keys instead of
 // thousands of scalar instructions: the kernel is latency-bound, so instruction count is what matters.
-// grid = (q_heads), block = 128; q_rows <= 32; head_dim a multiple of 16, <= 64.
-// dynamic shared memory = kv16 * (head_dim + 2) * 2 (K) + head_dim * (kv16 + 2) * 2 (V^T) + merge area
-//   4 * 32 * (head_dim + 2) * 4, kv16 = kv_rows rounded up to 16.
-extern "C" __global__ void __launch_bounds__(128)
+// grid = (q_heads, ceil(q_rows / 16)), block = 256; head_dim a multiple of 16, <= 64.
+// dynamic shared memory = 2 * kv16 * (head_dim + 8) * 2 (K and V) + merge area 8 * 16 * (head_dim + 2) * 4,
+// kv16 = kv_rows rounded up to 16.
+extern "C" __global__ void __launch_bounds__(256)
 agi_attention_mma_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, unsigned q_rows, unsigned kv_rows,
                        unsigned q_heads, unsigned kv_heads, unsigned head_dim, unsigned q_stride, unsigned k_stride,
                        unsigned v_stride, unsigned o_stride, float scale, unsigned mask_mode, unsigned mask_arg) {
@@ -412,39 +412,39 @@ agi_attention_mma_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, uns
   grid_dependency_wait();
   const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
   const unsigned head = blockIdx.x, kv_head = head / (q_heads / kv_heads);
+  const unsigned row_base = blockIdx.y * 16;   // this block's query rows
   const unsigned kv16 = (kv_rows + 15) & ~15u;
-  const unsigned k_pitch = head_dim + 2;   // elements; odd word count: the 8 key rows of a fragment hit 8 banks
-  const unsigned vt_pitch = kv16 + 2;
-  bf16* k_tile = reinterpret_cast<bf16*>(attn_smem);               // [kv16][k_pitch]
-  bf16* vt_tile = k_tile + size_t(kv16) * k_pitch;                 // [head_dim][vt_pitch]  (V transposed)
-  float* merge = reinterpret_cast<float*>(vt_tile + size_t(head_dim) * vt_pitch + ((size_t(head_dim) * vt_pitch) & 1));
+  // K and V both row-major with a pitch of head_dim + 8 elements: rows stay 16-byte aligned (cp.async,
+  // ldmatrix) and the eight rows a fragment touches fall into different banks.
+  const unsigned pitch = head_dim + 8;
+  bf16* k_tile = reinterpret_cast<bf16*>(attn_smem);               // [kv16][pitch]
+  bf16* v_tile = k_tile + size_t(kv16) * pitch;                    // [kv16][pitch]
+  float* merge = reinterpret_cast<float*>(v_tile + size_t(kv16) * pitch);
 
-  // ---- stage K (row-major) and V (transposed); rows past kv_rows are zero ----
+  // ---- stage K and V with 16-byte asynchronous copies, all in flight at once; rows past kv_rows are zero-filled ----
   const unsigned vec_per_row = head_dim / 8;
   for (unsigned i = threadIdx.x; i < kv16 * vec_per_row; i += blockDim.x) {
     const unsigned j = i / vec_per_row, d = (i % vec_per_row) * 8;
-    uint4 kk = make_uint4(0, 0, 0, 0), vv = kk;
-    if (j < kv_rows) {
-      kk = __ldg(reinterpret_cast<const uint4*>(k + size_t(j) * k_stride + kv_head * head_dim + d));
-      vv = __ldg(reinterpret_cast<const uint4*>(v + size_t(j) * v_stride + kv_head * head_dim + d));
-    }
-    unsigned* kd = reinterpret_cast<unsigned*>(&k_tile[j * k_pitch + d]);
-    kd[0] = kk.x; kd[1] = kk.y; kd[2] = kk.z; kd[3] = kk.w;
-    const bf16* ve = reinterpret_cast<const bf16*>(&vv);
-#pragma unroll
-    for (int e = 0; e < 8; ++e) vt_tile[(d + e) * vt_pitch + j] = ve[e];
+    const unsigned src_row = min(j, kv_rows - 1), bytes = j < kv_rows ? 16u : 0u;
+    const unsigned kd = static_cast<unsigned>(__cvta_generic_to_shared(k_tile + j * pitch + d));
+    const unsigned vd = static_cast<unsigned>(__cvta_generic_to_shared(v_tile + j * pitch + d));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(kd),
+                 "l"(k + size_t(src_row) * k_stride + kv_head * head_dim + d), "r"(bytes) : "memory");
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vd),
+                 "l"(v + size_t(src_row) * v_stride + kv_head * head_dim + d), "r"(bytes) : "memory");
   }
+  asm volatile("cp.async.commit_group;" ::: "memory");
   // ---- Q fragments (A operand), pre-scaled: rows g, g + 8 of each 16-row tile; zero past q_rows ----
   const unsigned ksteps = head_dim / 16;   // <= 4
-  unsigned qa[2][4][4];
+  unsigned qa[1][4][4];
 #pragma unroll
-  for (int mt = 0; mt < 2; ++mt)
+  for (int mt = 0; mt < 1; ++mt)
 #pragma unroll
     for (int ks = 0; ks < 4; ++ks)
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
         qa[mt][ks][r] = 0;
-        const unsigned row = mt * 16 + g + (r & 1) * 8, col = ks * 16 + 2 * t + (r >> 1) * 8;
+        const unsigned row = row_base + g + (r & 1) * 8, col = ks * 16 + 2 * t + (r >> 1) * 8;
         if (ks < ksteps && row < q_rows) {
           const bf162 pair = *reinterpret_cast<const bf162*>(q + size_t(row) * q_stride + head * head_dim + col);
           const float2 f = __bfloat1622float2(pair);
@@ -452,12 +452,13 @@ agi_attention_mma_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, uns
           qa[mt][ks][r] = *reinterpret_cast<const unsigned*>(&scaled);
         }
       }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
   __syncthreads();
 
   // running softmax state of this thread's 4 rows (mt 0/1 x rows g, g + 8) and its output accumulators
-  float row_max[2][2], row_sum[2][2], out[2][8][4];
+  float row_max[1][2], row_sum[1][2], out[1][8][4];
 #pragma unroll
-  for (int mt = 0; mt < 2; ++mt) {
+  for (int mt = 0; mt < 1; ++mt) {
     row_max[mt][0] = row_max[mt][1] = -3.0e38f;
     row_sum[mt][0] = row_sum[mt][1] = 0.f;
 #pragma unroll
@@ -466,9 +467,8 @@ agi_attention_mma_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, uns
       for (int i = 0; i < 4; ++i) out[mt][nt][i] = 0.f;
   }
   const unsigned dtiles = head_dim / 8;    // <= 8
-  const unsigned m_tiles = q_rows > 16 ? 2 : 1;
 
-  for (unsigned key0 = warp * 16; key0 < kv16; key0 += 64) {   // this warp's 16-key blocks
+  for (unsigned key0 = warp * 16; key0 < kv16; key0 += 128) {   // this warp's 16-key blocks
     // B fragments of K for the two 8-key tiles: b0 = (d 2t..2t+1, key g), b1 = (d 2t+8.., key g)
     unsigned kb[2][4][2];
 #pragma unroll
@@ -476,13 +476,12 @@ agi_attention_mma_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, uns
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks)
         if (ks < ksteps) {
-          const bf16* row = k_tile + (key0 + half * 8 + g) * k_pitch + ks * 16 + 2 * t;
+          const bf16* row = k_tile + (key0 + half * 8 + g) * pitch + ks * 16 + 2 * t;
           kb[half][ks][0] = *reinterpret_cast<const unsigned*>(row);
           kb[half][ks][1] = *reinterpret_cast<const unsigned*>(row + 8);
         }
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt) {
-      if (mt >= m_tiles) break;
+    for (int mt = 0; mt < 1; ++mt) {
       float s[2][4];
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
@@ -497,7 +496,7 @@ agi_attention_mma_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, uns
       for (int half = 0; half < 2; ++half)
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const unsigned key = key0 + half * 8 + 2 * t + (i & 1), row = mt * 16 + g + (i >> 1) * 8;
+          const unsigned key = key0 + half * 8 + 2 * t + (i & 1), row = row_base + g + (i >> 1) * 8;
           bool visible = key < kv_rows;
           if (mask_mode == 1) visible = visible && key <= row + mask_arg;
           if (mask_mode == 2) visible = visible && key / mask_arg == row / mask_arg;
@@ -532,24 +531,26 @@ agi_attention_mma_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, uns
         pa[hr] = *reinterpret_cast<const unsigned*>(&lo);
         pa[2 + hr] = *reinterpret_cast<const unsigned*>(&hi);
       }
-      // O += P (16 x 16 keys) . V (16 keys x 8 dims) per 8-dim tile; V^T rows give contiguous key pairs
+      // O += P (16 x 16 keys) . V (16 keys x 8 dims) per 8-dim tile.  ldmatrix with transpose turns two
+      // 8 x 8 blocks of row-major V (keys 0-7 and 8-15 of this block) into the B fragment (key pair, dim g).
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt)
         if (nt < dtiles) {
-          const bf16* row = vt_tile + (nt * 8 + g) * vt_pitch + key0 + 2 * t;
-          const unsigned b0 = *reinterpret_cast<const unsigned*>(row), b1 = *reinterpret_cast<const unsigned*>(row + 8);
+          const unsigned addr = static_cast<unsigned>(__cvta_generic_to_shared(v_tile + (key0 + (lane & 15)) * pitch + nt * 8));
+          unsigned b0, b1;
+          asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(addr));
           skinny_mma_bf16(out[mt][nt], pa[0], pa[1], pa[2], pa[3], b0, b1);
         }
     }
   }
 
-  // ---- merge the four warps: [warp][row 0..31][head_dim + 2] with max and sum in the last two columns ----
+  // ---- merge the eight warps: [warp][row 0..15][head_dim + 2] with max and sum in the last two columns ----
   const unsigned mp = head_dim + 2;
 #pragma unroll
-  for (int mt = 0; mt < 2; ++mt)
+  for (int mt = 0; mt < 1; ++mt)
 #pragma unroll
     for (int hr = 0; hr < 2; ++hr) {
-      float* dst = merge + (size_t(warp) * 32 + mt * 16 + g + hr * 8) * mp;
+      float* dst = merge + (size_t(warp) * 16 + g + hr * 8) * mp;
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt)
         if (nt < dtiles) {
@@ -562,19 +563,20 @@ agi_attention_mma_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, uns
       }
     }
   __syncthreads();
-  for (unsigned i = threadIdx.x; i < q_rows * head_dim; i += blockDim.x) {
+  const unsigned my_rows = min(16u, q_rows - row_base);
+  for (unsigned i = threadIdx.x; i < my_rows * head_dim; i += blockDim.x) {
     const unsigned r = i / head_dim, d = i % head_dim;
     float best = -3.0e38f;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) best = fmaxf(best, merge[(w * 32 + r) * mp + head_dim]);
+    for (int w = 0; w < 8; ++w) best = fmaxf(best, merge[(w * 16 + r) * mp + head_dim]);
     float num = 0.f, den = 0.f;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const float* src = merge + (w * 32 + r) * mp;
+    for (int w = 0; w < 8; ++w) {
+      const float* src = merge + (w * 16 + r) * mp;
       const float f = src[head_dim] > -1.0e38f ? __expf(src[head_dim] - best) : 0.f;
       num += f * src[d];
       den += f * src[head_dim + 1];
     }
-    o[size_t(r) * o_stride + head * head_dim + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+    o[size_t(row_base + r) * o_stride + head * head_dim + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
   }
 }

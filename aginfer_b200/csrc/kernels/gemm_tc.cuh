@@ -139,9 +139,11 @@ __device__ __forceinline__ void tmem_load16(unsigned addr, float v[16]) {
 }
 
 // Thread-block cluster helpers (split-K slices of one output tile form a cluster along grid z).
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_sync() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  cluster_arrive();
+  cluster_wait();
 }
 // Address of `local_smem_addr` in the shared memory of cluster rank `rank`.
 __device__ __forceinline__ unsigned peer_smem(unsigned local_smem_addr, unsigned rank) {
@@ -209,17 +211,33 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
   tc_fence_after();
   const unsigned tmem_base = tmem_slot;
   // Cluster split-K: every slice must be running (its shared memory live) before anyone writes into it.
+  // Arrive now, wait only just before the first remote store: by then the barrier has long completed.
   if (warp == 0) TC_STAMP(33);
-  if (kCluster > 1) cluster_sync();
+  if (kCluster > 1) cluster_arrive();
   if (warp == 0) TC_STAMP(34);
 
+  // Weights do not depend on the previous kernel: the weight tiles of the first ring slots are requested
+  // before the grid-dependency wait (they join the first commit group below).
+  const size_t w_row_bytes = size_t(K) * elem, x_row_bytes = size_t(ldx) * elem;
+  const unsigned early = min(stages, nkb);
+  auto load_weights = [&](unsigned i) {
+    const size_t k_byte = size_t(kb_begin + i) * kRowBytes;
+    const unsigned a_base = ring + (i % stages) * stage_bytes;
+#pragma unroll
+    for (unsigned j = 0; j < 8; ++j) {
+      const unsigned idx = tid + j * kProducers, r = idx >> 3, c = idx & 7;
+      const unsigned row = min(n0 + r, N - 1);  // rows past N are loaded from the last row and never stored
+      cp_async_16(a_base + r * kRowBytes + ((c ^ (r & 7)) << 4), w + row * w_row_bytes + k_byte + (c << 4));
+    }
+  };
+  if (warp < 4)
+    for (unsigned i = 0; i < early; ++i) load_weights(i);
+
   grid_dependency_wait();
-  grid_dependency_release();
   if (warp == 0) TC_STAMP(35);
 
   if (warp < 4) {
     // ---------------- producers ----------------
-    const size_t w_row_bytes = size_t(K) * elem, x_row_bytes = size_t(ldx) * elem;
     const unsigned b_chunks = TN * 8;
     for (unsigned i = 0; i < nkb + kLag; ++i) {
       if (i < nkb) {
@@ -227,12 +245,7 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
         if (round > 0) mbar_wait(&empty_bar[s], (round - 1) & 1, status, kTimeoutEmpty | s);
         const size_t k_byte = size_t(kb_begin + i) * kRowBytes;
         const unsigned a_base = ring + s * stage_bytes, b_base = a_base + kATileBytes;
-#pragma unroll
-        for (unsigned j = 0; j < 8; ++j) {
-          const unsigned idx = tid + j * kProducers, r = idx >> 3, c = idx & 7;
-          const unsigned row = min(n0 + r, N - 1);  // rows past N are loaded from the last row and never stored
-          cp_async_16(a_base + r * kRowBytes + ((c ^ (r & 7)) << 4), w + row * w_row_bytes + k_byte + (c << 4));
-        }
+        if (i >= early) load_weights(i);
         for (unsigned idx = tid; idx < b_chunks; idx += kProducers) {
           const unsigned r = idx >> 3, c = idx & 7;
           const unsigned row = min(m0 + r, M - 1);
@@ -265,6 +278,7 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
     }
     if (lane == 0) tc_commit(&accum_bar);
     __syncwarp();
+    if (kCluster > 1) cluster_wait();  // every thread pairs its early arrive with one wait
   }
 
   // ---------------- epilogue (warps 0-3: TMEM lanes 32 * warp ... +31) ----------------
@@ -276,7 +290,9 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
     const unsigned n = n0 + warp * 32 + lane;
     const float alpha = (flags & kFlagScaled) ? (*scale_a) * (*scale_w) : 1.f;
     const unsigned lane_addr = tmem_base + ((warp * 32u) << 16);
+    if (kCluster > 1) cluster_wait();  // peers are running: their gather buffers may be written
     for (unsigned c0 = 0; c0 < TN; c0 += 16) {
+      if (kCluster > 1 && m0 + c0 >= M) break;  // token columns past M carry nothing
       float v[16];
       if (nkb > 0) {
         tmem_load16(lane_addr + c0, v);
@@ -311,17 +327,37 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
   }
   if (kCluster > 1) {
     // ---------------- split-K inside a cluster: partial sums travelled through distributed shared memory ----
-    cluster_sync();  // every slice's stores into this CTA's gather buffer are complete and visible
+    // This rank finishes tokens split, split + C, ...: their bias and residual values are fetched while the
+    // cluster barrier completes.
+    constexpr int kMine = (64 + kCluster - 1) / kCluster;   // at most 64 tokens in cluster mode
+    const unsigned n = n0 + warp * 32 + lane;
+    const unsigned my_tokens = warp < 4 && n < N && split < min(TN, M - m0)
+                                   ? (min(TN, M - m0) - split + kCluster - 1) / kCluster : 0;
+    bf16 early_bias = __float2bfloat16_rn(0.f), early_res[kMine];
+    if (my_tokens != 0 && (flags & kFlagBias)) early_bias = bias[n];
+#pragma unroll
+    for (int j = 0; j < kMine; ++j)
+      if (unsigned(j) < my_tokens && (flags & kFlagResidual))
+        early_res[j] = residual[size_t(m0 + split + j * kCluster) * ldy + n];
+    cluster_arrive();
+    cluster_wait();  // every slice's stores into this CTA's gather buffer are complete and visible
     if (warp == 0) TC_STAMP(39);
-    if (warp < 4) {
-      const unsigned n = n0 + warp * 32 + lane;
+    if (my_tokens != 0) {
       const float alpha = (flags & kFlagScaled) ? (*scale_a) * (*scale_w) : 1.f;
       const float* mine = reinterpret_cast<const float*>(dynamic_smem + (gather_base - smem_u32(dynamic_smem)));
-      for (unsigned j = 0; split + j * kCluster < min(TN, M - m0); ++j) {  // this rank's tokens: split, split + C, ...
+#pragma unroll
+      for (int j = 0; j < kMine; ++j) {
+        if (unsigned(j) >= my_tokens) break;
         float total = 0.f;
 #pragma unroll
         for (int z = 0; z < kCluster; ++z) total += mine[((z * gather_cols) + j) * kTileN + warp * 32 + lane];  // slice order
-        if (n < N) gemm_store(total, m0 + split + j * kCluster, n, y, ldy, bias, residual, alpha, flags);
+        float r = total * alpha;
+        if (flags & kFlagBias) r += __bfloat162float(early_bias);
+        r = apply_activation(r, flags);
+        if (flags & kFlagResidual) r += __bfloat162float(early_res[j]);
+        const size_t at = size_t(m0 + split + j * kCluster) * ldy + n;
+        if (flags & kFlagOutF32) static_cast<float*>(y)[at] = r;
+        else static_cast<bf16*>(y)[at] = __float2bfloat16_rn(r);
       }
     }
     if (warp == 0) TC_STAMP(40);

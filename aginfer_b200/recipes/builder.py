@@ -82,6 +82,9 @@ ATTN_SMEM_BUDGET = 200 * 1024    # dynamic shared memory of the keys-in-shared-m
 # One bulk copy per operand into unpadded rows was measured slower than one copy per row into padded rows:
 # unpadded rows make every fragment read an 8-way bank conflict and shared-memory reads bound the MMA phase.
 USE_SLAB_COPIES = False
+# 16 weight rows per CTA use the whole 16-row MMA tile and halve the activation re-reads per weight byte; 8 rows
+# give twice as many CTAs.  16 is chosen when it still yields at least this many CTAs.
+STREAM_MIN_CTAS_FOR_16_ROWS = int(__import__('os').environ.get('AGI_STREAM_MIN16', SM_COUNT))
 STREAM_SM_BYTES = 220 * 1024     # shared memory the bulk-stream GEMM CTAs of one SM may use together
 STREAM_CTA_BYTES = 110 * 1024    # and the most a single CTA takes (two CTAs per SM keep one draining while one fills)
 
@@ -135,7 +138,7 @@ def stream_tiling(M: int, N: int, K: int, elem: int, extra_rows: int = 0, contig
     memory of an SM split evenly between the CTAs that share it, so that as many bytes as possible are
     in flight.  16 rows per CTA halve the activation traffic per weight byte and are used when N is large
     enough to still give every SM a CTA."""
-    rows = 16 if ceil_div(N, 16) >= SM_COUNT else 8
+    rows = 16 if ceil_div(N, 16) >= STREAM_MIN_CTAS_FOR_16_ROWS else 8
     grid = ceil_div(N, rows)
     per_sm = ceil_div(grid, SM_COUNT)
     tiles = next(v for v in (1, 2, 3, 4, 6, 8) if 8 * v >= M)
@@ -315,11 +318,11 @@ class RecipeBuilder:
         rows_smem = (ceil_div(kv_rows * (head_dim + 2), 8) * 16 + kv_rows * head_dim * 2 + q_rows * head_dim * 4
                      + q_rows * ceil_div(kv_rows, 32) * 32 * 4 + 8 * q_rows * head_dim * 4 + 2 * 8 * q_rows * 4)
         kv16 = ceil_div(kv_rows, 16) * 16
-        mma_smem = kv16 * (head_dim + 2) * 2 + head_dim * (kv16 + 2) * 2 + 8 + 4 * 32 * (head_dim + 2) * 4
-        if (aligned and q_rows <= 32 and head_dim <= 64 and head_dim % 16 == 0 and q_stride % 2 == 0
+        mma_smem = 2 * kv16 * (head_dim + 8) * 2 + 8 * 16 * (head_dim + 2) * 4
+        if (aligned and q_rows <= 64 and head_dim <= 64 and head_dim % 16 == 0 and q_stride % 2 == 0
                 and mma_smem <= ATTN_SMEM_BUDGET and algorithm in ("auto", "mma")):
             # few query rows: one block per head, tensor-core scores and P.V
-            self.launch("agi_attention_mma_bf16", (q_heads, 1, 1), (128, 1, 1), args, shared_bytes=mma_smem,
+            self.launch("agi_attention_mma_bf16", (q_heads, ceil_div(q_rows, 16), 1), (256, 1, 1), args, shared_bytes=mma_smem,
                         op=f"attention_{mask}", algorithm="mma_key_split")
             return
         if (aligned and q_rows <= 32 and head_dim <= 64 and rows_smem <= ATTN_SMEM_BUDGET
