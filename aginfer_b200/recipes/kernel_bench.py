@@ -16,11 +16,14 @@ import tempfile
 from pathlib import Path
 
 D, T, MLP, LAYERS = 1536, 17, 6144, 16
-GEMM_SHAPES = {"gemm_q": (D, D), "gemm_fc1": (MLP, D), "gemm_fc2": (D, MLP)}
+GEMM_SHAPES = {"gemm_q": (D, D), "gemm_fc1": (MLP, D), "gemm_fc2": (D, MLP),
+               # the (N, K) grid of the FP8 GEMM sweep
+               "gemm_2048x2048": (2048, 2048), "gemm_11008x2048": (11008, 2048), "gemm_2048x11008": (2048, 11008),
+               "gemm_2560x2048": (2560, 2048), "gemm_1536x1536": (1536, 1536), "gemm_6144x1536": (6144, 1536)}
 CASES = ("empty", "layernorm", "attn_self", "attn_cross", *GEMM_SHAPES)
 
 
-def build(case: str, tactic: str, reps: int, tokens: int, stages: int = 4):
+def build(case: str, tactic: str, reps: int, tokens: int, stages: int = 4, dtype: str = "bf16"):
     import torch
 
     from . import Arena, RecipeBuilder, Tensor, U32, Weight, io
@@ -31,10 +34,14 @@ def build(case: str, tactic: str, reps: int, tokens: int, stages: int = 4):
         n, k = GEMM_SHAPES[case]
         g = torch.Generator().manual_seed(0)
         for l in range(LAYERS):
-            weights[f"l{l}.w"] = (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16)
+            w = torch.randn(n, k, generator=g) * 0.02
+            weights[f"l{l}.w"] = w.to(torch.bfloat16) if dtype == "bf16" else w.clamp(-0.08, 0.08).mul(448 / 0.08).to(
+                torch.float8_e4m3fn)
+        weights["w_scale"] = torch.tensor(0.08 / 448, dtype=torch.float32)
     r = RecipeBuilder(describe(weights))
     r.begin_profile("default", [io("token", "I32", [1])], [io("status", "I32", [1])])
-    x, y = r.alloc(64 * MLP * 2), r.alloc(64 * MLP * 2)
+    big = max(tokens, 64) * 11008 * 2
+    x, y, scale_a = r.alloc(big), r.alloc(big), r.alloc(4)
     kbuf, vbuf, q = r.alloc(300 * D * 2), r.alloc(300 * D * 2), r.alloc(64 * D * 2)
     for i in range(reps):
         if case == "empty":
@@ -47,7 +54,11 @@ def build(case: str, tactic: str, reps: int, tokens: int, stages: int = 4):
                         q_stride=D, k_stride=D, v_stride=D, o_stride=D)
         else:
             n, k = GEMM_SHAPES[case]
-            r.gemm(x, Weight(f"l{i % LAYERS}.w"), y, tokens, n, k, bias=Weight("bias"), tactic=tactic)
+            if dtype == "bf16":
+                r.gemm(x, Weight(f"l{i % LAYERS}.w"), y, tokens, n, k, tactic=tactic)
+            else:   # activations taken as already quantised bytes; scales are whatever the arena holds
+                r.gemm(x, Weight(f"l{i % LAYERS}.w"), y, tokens, n, k, dtype="e4m3", scale_a=scale_a,
+                       scale_w=Weight("w_scale"), tactic=tactic)
     r.export_status(Tensor("status"))
     return weights, r
 
@@ -66,10 +77,11 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--tokens", type=int, default=T)
     ap.add_argument("--pdl", action="store_true")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "e4m3"])
     ap.add_argument("--stages", type=int, default=4, help="K partitions of the bulk-stream GEMM (1-4)")
     args = ap.parse_args()
 
-    weights, recipe = build(args.case, args.tactic, args.reps, args.tokens, args.stages)
+    weights, recipe = build(args.case, args.tactic, args.reps, args.tokens, args.stages, args.dtype)
     with tempfile.TemporaryDirectory() as tmp:
         aim = build_aim(Path(tmp), weights, recipe)
         runner = Runner(aim, flags=rt.PROGRAMMATIC_LAUNCH if args.pdl else 0)
@@ -90,8 +102,10 @@ def main() -> None:
         line = f"{args.case} tactic={args.tactic} tokens={args.tokens} pdl={args.pdl}: {us:.2f} us/launch"
         if args.case in GEMM_SHAPES:
             n, k = GEMM_SHAPES[args.case]
-            line += f", {n * k * 2 / us / 1e3:.0f} GB/s of weights"
-            line += " (L2-resident rotation)" if n * k * 2 * LAYERS < 126e6 else " (rotation larger than L2)"
+            elem = 2 if args.dtype == "bf16" else 1
+            line += f" dtype={args.dtype}, {n * k * elem / us / 1e3:.0f} GB/s of weights"
+            line += f", {2.0 * args.tokens * n * k / us / 1e6:.1f} TFLOP/s"
+            line += " (L2-resident rotation)" if n * k * elem * LAYERS < 126e6 else " (rotation larger than L2)"
         print(line + f", status={status.item()}")
 
 
