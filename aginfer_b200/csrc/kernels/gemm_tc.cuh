@@ -161,6 +161,88 @@ __device__ __forceinline__ unsigned tmem_columns_for(unsigned tokens) {
   return c;
 }
 
+// Epilogue of one thread for 16 consecutive tokens of its output feature: scale, bias, activation,
+// residual, store.  Written as whole-array passes (flag tests once per 16 values, loads before
+// uses) because only four warps run it: every dependent instruction chain is paid in full.
+template <bool kOutF32, bool kFull>
+__device__ __forceinline__ void store_tokens16(const float v[16], unsigned count, void* y, const bf16* residual,
+                                               size_t offset, unsigned ldy, float alpha, float bias_v, unsigned flags) {
+  float r[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) r[i] = fmaf(v[i], alpha, bias_v);
+  const unsigned act = flags & kFlagActMask;
+  if (act == kActGeluTanh) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) r[i] = gelu_tanh(r[i]);
+  } else if (act == kActSilu) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) r[i] = silu(r[i]);
+  } else if (act == kActRelu) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) r[i] = fmaxf(r[i], 0.f);
+  }
+  if (flags & kFlagResidual) {
+    bf16 res[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (kFull || unsigned(i) < count) res[i] = residual[offset + size_t(i) * ldy];
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (kFull || unsigned(i) < count) r[i] += __bfloat162float(res[i]);
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    if (!kFull && unsigned(i) >= count) continue;
+    if (kOutF32) static_cast<float*>(y)[offset + size_t(i) * ldy] = r[i];
+    else static_cast<bf16*>(y)[offset + size_t(i) * ldy] = __float2bfloat16_rn(r[i]);
+  }
+}
+
+// Split-K finish of one thread: four consecutive output features of one token.  Vector loads and stores
+// when the row pitch keeps them aligned, the scalar path otherwise (and at the ragged edge of N).
+__device__ __forceinline__ void store_features4(const float t4[4], unsigned m, unsigned n, unsigned N, void* y,
+                                                unsigned ldy, const bf16* bias, const bf16* residual, float alpha,
+                                                unsigned flags) {
+  const size_t at = size_t(m) * ldy + n;
+  const bool aligned = ((reinterpret_cast<size_t>(y) | reinterpret_cast<size_t>(bias) |
+                         reinterpret_cast<size_t>(residual)) & 15) == 0;  // unused pointers are arena-aligned
+  if (n + 3 < N && (ldy & 3) == 0 && aligned) {
+    float r[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) r[j] = t4[j] * alpha;
+    if (flags & kFlagBias) {
+      const uint2 b = *reinterpret_cast<const uint2*>(bias + n);
+      const float2 b01 = __bfloat1622float2(*reinterpret_cast<const bf162*>(&b.x));
+      const float2 b23 = __bfloat1622float2(*reinterpret_cast<const bf162*>(&b.y));
+      r[0] += b01.x; r[1] += b01.y; r[2] += b23.x; r[3] += b23.y;
+    }
+    const unsigned act = flags & kFlagActMask;
+    if (act != 0) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) r[j] = apply_activation(r[j], flags);
+    }
+    if (flags & kFlagResidual) {
+      const uint2 q = *reinterpret_cast<const uint2*>(residual + at);
+      const float2 q01 = __bfloat1622float2(*reinterpret_cast<const bf162*>(&q.x));
+      const float2 q23 = __bfloat1622float2(*reinterpret_cast<const bf162*>(&q.y));
+      r[0] += q01.x; r[1] += q01.y; r[2] += q23.x; r[3] += q23.y;
+    }
+    if (flags & kFlagOutF32) {
+      *reinterpret_cast<float4*>(static_cast<float*>(y) + at) = make_float4(r[0], r[1], r[2], r[3]);
+    } else {
+      const bf162 lo = __floats2bfloat162_rn(r[0], r[1]), hi = __floats2bfloat162_rn(r[2], r[3]);
+      uint2 out;
+      out.x = *reinterpret_cast<const unsigned*>(&lo);
+      out.y = *reinterpret_cast<const unsigned*>(&hi);
+      *reinterpret_cast<uint2*>(static_cast<bf16*>(y) + at) = out;
+    }
+    return;
+  }
+#pragma unroll
+  for (unsigned j = 0; j < 4; ++j)
+    if (n + j < N) gemm_store(t4[j], m, n + j, y, ldy, bias, residual, alpha, flags);
+}
+
 // grid = (ceil(N / 128), ceil(M / TN), splits), block = 160 threads,
 // dynamic shared memory = stages * (16384 + TN * 128) + 1024.
 template <bool kFp8, int kCluster = 1>
@@ -220,15 +302,23 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
   // before the grid-dependency wait (they join the first commit group below).
   const size_t w_row_bytes = size_t(K) * elem, x_row_bytes = size_t(ldx) * elem;
   const unsigned early = min(stages, nkb);
+  // A producer thread copies chunk c of rows r0, r0 + 16, ...: the swizzled destination differs from row
+  // to row by a constant (16 rows = 2048 B, and r & 7 does not change), the source by 16 row pitches, so
+  // one copy costs an add, not an address computation.  Rows past the matrix are skipped: what the
+  // tensor core reads there only reaches accumulator rows / columns that are never stored.
+  const unsigned r0 = tid >> 3, chunk = tid & 7;
+  const unsigned dst_off = r0 * kRowBytes + ((chunk ^ (r0 & 7)) << 4);
+  const unsigned a_rows = n0 + r0 < N ? (min(kTileN, N - n0) - r0 + 15) / 16 : 0;
+  const unsigned b_rows = (m0 + r0 < M && r0 < TN) ? (min(TN, M - m0) - r0 + 15) / 16 : 0;
+  const uint8_t* w_src = w + size_t(n0 + r0) * w_row_bytes + size_t(kb_begin) * kRowBytes + (chunk << 4);
+  const uint8_t* x_src = x + size_t(m0 + r0) * x_row_bytes + size_t(kb_begin) * kRowBytes + (chunk << 4);
+  const size_t w_step = 16 * w_row_bytes, x_step = 16 * x_row_bytes;
   auto load_weights = [&](unsigned i) {
-    const size_t k_byte = size_t(kb_begin + i) * kRowBytes;
-    const unsigned a_base = ring + (i % stages) * stage_bytes;
+    const uint8_t* src = w_src + size_t(i) * kRowBytes;
+    const unsigned dst = ring + (i % stages) * stage_bytes + dst_off;
 #pragma unroll
-    for (unsigned j = 0; j < 8; ++j) {
-      const unsigned idx = tid + j * kProducers, r = idx >> 3, c = idx & 7;
-      const unsigned row = min(n0 + r, N - 1);  // rows past N are loaded from the last row and never stored
-      cp_async_16(a_base + r * kRowBytes + ((c ^ (r & 7)) << 4), w + row * w_row_bytes + k_byte + (c << 4));
-    }
+    for (unsigned j = 0; j < 8; ++j)
+      if (j < a_rows) cp_async_16(dst + j * 2048, src + j * w_step);
   };
   if (warp < 4)
     for (unsigned i = 0; i < early; ++i) load_weights(i);
@@ -238,23 +328,24 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
 
   if (warp < 4) {
     // ---------------- producers ----------------
-    const unsigned b_chunks = TN * 8;
     for (unsigned i = 0; i < nkb + kLag; ++i) {
       if (i < nkb) {
         const unsigned s = i % stages, round = i / stages;
+        if (warp == 0 && i == 8) TC_STAMP(41);
         if (round > 0) mbar_wait(&empty_bar[s], (round - 1) & 1, status, kTimeoutEmpty | s);
-        const size_t k_byte = size_t(kb_begin + i) * kRowBytes;
-        const unsigned a_base = ring + s * stage_bytes, b_base = a_base + kATileBytes;
+        if (warp == 0 && i == 8) TC_STAMP(42);
         if (i >= early) load_weights(i);
-        for (unsigned idx = tid; idx < b_chunks; idx += kProducers) {
-          const unsigned r = idx >> 3, c = idx & 7;
-          const unsigned row = min(m0 + r, M - 1);
-          cp_async_16(b_base + r * kRowBytes + ((c ^ (r & 7)) << 4), x + row * x_row_bytes + k_byte + (c << 4));
-        }
+        const uint8_t* src = x_src + size_t(i) * kRowBytes;
+        const unsigned dst = ring + s * stage_bytes + kATileBytes + dst_off;
+#pragma unroll
+        for (unsigned j = 0; j < 16; ++j)
+          if (j < b_rows) cp_async_16(dst + j * 2048, src + j * x_step);
       }
       cp_async_commit();  // an empty group past the end keeps the wait arithmetic uniform
+      if (warp == 0 && i == 8) TC_STAMP(43);
       if (i >= kLag) {
         cp_async_wait<kLag>();
+        if (warp == 0 && i == 8) TC_STAMP(44);
         fence_async_shared();
         mbar_arrive(&full_bar[(i - kLag) % stages]);
       }
@@ -264,7 +355,10 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
     const unsigned idesc = instr_descriptor<kFp8>(TN);
     for (unsigned i = 0; i < nkb; ++i) {
       const unsigned s = i % stages, round = i / stages;
+      if (i == 8) TC_STAMP(45);
       mbar_wait(&full_bar[s], round & 1, status, kTimeoutFull | s);
+      if (i == 0) TC_STAMP(46);
+      if (i == 8) TC_STAMP(47);
       tc_fence_after();
       if (lane == 0) {
         const unsigned a_base = ring + s * stage_bytes, b_base = a_base + kATileBytes;
@@ -289,6 +383,7 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
     tc_fence_after();
     const unsigned n = n0 + warp * 32 + lane;
     const float alpha = (flags & kFlagScaled) ? (*scale_a) * (*scale_w) : 1.f;
+    const float bias_v = ((flags & kFlagBias) && n < N) ? __bfloat162float(bias[n]) : 0.f;
     const unsigned lane_addr = tmem_base + ((warp * 32u) << 16);
     if (kCluster > 1) cluster_wait();  // peers are running: their gather buffers may be written
     for (unsigned c0 = 0; c0 < TN; c0 += 16) {
@@ -300,7 +395,21 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
 #pragma unroll
         for (int i = 0; i < 16; ++i) v[i] = 0.f;
       }
-      if (n < N) {
+      if (kCluster == 1 && splits == 1) {
+        // direct store: bias was fetched once per thread, flags are tested once per 16 tokens
+        if (n < N && m0 + c0 < M) {
+          const unsigned count = min(16u, M - (m0 + c0));
+          const size_t offset = size_t(m0 + c0) * ldy + n;
+          const bool f32 = (flags & kFlagOutF32) != 0;
+          if (count == 16) {
+            if (f32) store_tokens16<true, true>(v, 16, y, residual, offset, ldy, alpha, bias_v, flags);
+            else store_tokens16<false, true>(v, 16, y, residual, offset, ldy, alpha, bias_v, flags);
+          } else {
+            if (f32) store_tokens16<true, false>(v, count, y, residual, offset, ldy, alpha, bias_v, flags);
+            else store_tokens16<false, false>(v, count, y, residual, offset, ldy, alpha, bias_v, flags);
+          }
+        }
+      } else if (n < N) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           const unsigned m = m0 + c0 + i;
@@ -311,8 +420,7 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
             const unsigned c = c0 + i, owner = c % kCluster;
             const unsigned cell = gather_base + (((split * gather_cols) + c / kCluster) * kTileN + warp * 32 + lane) * 4;
             store_peer_f32(peer_smem(cell, owner), v[i]);
-          } else if (splits == 1) gemm_store(v[i], m, n, y, ldy, bias, residual, alpha, flags);
-          else __stcg(partial + (size_t(split) * M + m) * Np + n, v[i]);
+          } else __stcg(partial + (size_t(split) * M + m) * Np + n, v[i]);
         }
       }
     }
@@ -396,9 +504,7 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
           total.x += part[z].x; total.y += part[z].y; total.z += part[z].z; total.w += part[z].w;
         }
       const float t4[4] = {total.x, total.y, total.z, total.w};
-#pragma unroll
-      for (unsigned j = 0; j < 4; ++j)
-        if (n + j < N) gemm_store(t4[j], m, n + j, y, ldy, bias, residual, alpha, flags);
+      store_features4(t4, m, n, N, y, ldy, bias, residual, alpha, flags);
     }
   }
   if (tid == 0) counters[tile] = 0;

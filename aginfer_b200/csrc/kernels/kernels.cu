@@ -6,5 +6,6 @@
 #include "attention.cuh"
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
+#include "gemm_tc_wide.cuh"
 #include "gemm_skinny.cuh"
 #include "gemm_stream.cuh"

@@ -77,7 +77,7 @@ def ceil_div(a: int, b: int) -> int:
 
 TC_SCRATCH_BYTES = 32 << 20    # fp32 partial tiles of split-K tensor-core GEMMs, [slice][M][N]
 TC_COUNTER_BYTES = 16 << 10    # per-tile arrival counters of the same
-TC_SMEM_BUDGET = 200 * 1024    # dynamic shared memory a tensor-core GEMM CTA may use
+TC_SMEM_BUDGET = 225 * 1024     # ring bytes per CTA: 227 KB opt-in limit minus barriers and alignment slack
 ATTN_SMEM_BUDGET = 200 * 1024    # dynamic shared memory of the keys-in-shared-memory attention kernel
 # One bulk copy per operand into unpadded rows was measured slower than one copy per row into padded rows:
 # unpadded rows make every fragment read an 8-way bank conflict and shared-memory reads bound the MMA phase.
@@ -107,6 +107,50 @@ def tc_tiling(M: int, N: int, K: int, elem: int, splits: int | None = None) -> d
             "shared_bytes": stages * stage_bytes + 1024}
 
 
+def tc_prefill_plan(M: int, N: int, K: int, elem: int) -> dict[str, int]:
+    """Tile shape for a tensor-core GEMM over many tokens: weight rows per CTA (128, or 256 = the wide kernel
+    with two accumulators), token tile TN, K slices.
+
+    The kernels fill shared memory from L2 with 16-byte asynchronous copies, measured at about 32 bytes per
+    clock and SM, which is slower than the tensor core consumes it; so the estimate per CTA is
+    K blocks x max(fill, MMA) + set-up + epilogue, times the number of waves over 148 SMs, plus the
+    slab pass of the finishing CTA when K is sliced.  The cheapest candidate wins."""
+    k_blocks = K * elem // 128
+    best: dict[str, int] | None = None
+    for rows in (128, 256):
+        if rows == 256 and N < 256:
+            continue
+        n_tiles = ceil_div(N, rows)
+        seen = set()
+        for cap in range(256, 48, -16):
+            m_tiles = ceil_div(M, cap)
+            TN = ceil_div(ceil_div(M, m_tiles), 16) * 16
+            if TN in seen:
+                continue
+            seen.add(TN)
+            for splits in (1, 2, 3, 4, 6, 8):
+                per = ceil_div(k_blocks, splits)
+                if ceil_div(k_blocks, per) != splits or (splits > 1 and per < 4):
+                    continue
+                if splits > 1 and splits * M * n_tiles * rows * 4 > TC_SCRATCH_BYTES:
+                    continue
+                if n_tiles * m_tiles * 4 > TC_COUNTER_BYTES:
+                    continue
+                stage_bytes = rows * 128 + TN * 128
+                fill = stage_bytes / 28
+                mma = (rows // 128) * TN * 2
+                ctas = n_tiles * m_tiles * splits
+                cost = ceil_div(ctas, SM_COUNT) * (per * max(fill, mma) + 5000 + TN * 25)
+                if splits > 1:      # slab stores of every slice, then one CTA per tile reads them all back
+                    cost += 4000 + rows * TN * (splits + 1) // 8
+                if best is None or cost < best["cost"]:
+                    stages = max(3, min(12, TC_SMEM_BUDGET // stage_bytes, max(per, 3)))
+                    best = {"rows": rows, "TN": TN, "m_tiles": m_tiles, "n_tiles": n_tiles, "splits": splits,
+                            "stages": stages, "shared_bytes": stages * stage_bytes + 1024, "cost": int(cost)}
+    assert best is not None
+    return best
+
+
 TC_CLUSTER_SIZES = {"bf16": (2, 3, 4, 6, 8), "e4m3": (2, 4, 8)}   # compiled cluster variants
 
 
@@ -126,9 +170,10 @@ def tc_cluster_tiling(M: int, N: int, K: int, elem: int, dtype: str = "bf16") ->
     if ceil_div(k_blocks, per) != cluster:      # every rank of the cluster must own a non-empty slice
         return None
     stage_bytes = 16384 + TN * 128
-    stages = max(3, min(12, TC_SMEM_BUDGET // stage_bytes, per))
+    gather_bytes = cluster * ceil_div(TN, cluster) * 512
+    stages = max(3, min(12, (TC_SMEM_BUDGET - gather_bytes) // stage_bytes, per))
     return {"TN": TN, "n_tiles": n_tiles, "cluster": cluster, "stages": stages,
-            "shared_bytes": stages * stage_bytes + 1024 + cluster * ceil_div(TN, cluster) * 512}
+            "shared_bytes": stages * stage_bytes + 1024 + gather_bytes}
 
 
 def stream_tiling(M: int, N: int, K: int, elem: int, extra_rows: int = 0, contiguous: bool = True) -> dict[str, int]:
@@ -364,7 +409,7 @@ class RecipeBuilder:
             if M <= 64 and (K * elem) % 64 == 0 and aligned:
                 tactic = "stream"
             elif (K * elem) % 128 == 0 and aligned:
-                tactic = "tcgen05"
+                tactic = "tcgen05_plan" if M >= 128 else "tcgen05"
             else:
                 tactic = "simt"
         if tactic == "stream":
@@ -403,14 +448,34 @@ class RecipeBuilder:
                         shared_bytes=t["shared_bytes"], op=f"gemm_{dtype}",
                         algorithm=f"tcgen05_128x{t['TN']}_s{t['stages']}_cluster{t['cluster']}")
             return
-        if tactic != "tcgen05":
+        if tactic not in ("tcgen05", "tcgen05_wide", "tcgen05_plan"):
             raise ValueError(f"unknown GEMM tactic {tactic!r}")
         if (K * elem) % 128 or ((ldx or K) * elem) % 16:
             raise ValueError("tcgen05 GEMM needs K bytes % 128 == 0 and 16-byte aligned rows")
+        partial, counters = self._tc_scratch
+        tc_args = args[:7] + [partial, counters, Arena(STATUS_WORD)] + args[7:]
+        if tactic in ("tcgen05_wide", "tcgen05_plan"):
+            if tactic == "tcgen05_plan":
+                t = tc_prefill_plan(M, N, K, elem)
+            else:   # explicit: 256 rows, the largest token tile, K sliced only on request
+                m_tiles = ceil_div(M, 256)
+                TN = ceil_div(ceil_div(M, m_tiles), 16) * 16
+                k_blocks = K * elem // 128
+                per = ceil_div(k_blocks, max(1, min(splits or 1, 8, k_blocks)))
+                stage_bytes = 32768 + TN * 128
+                stages = max(3, min(12, TC_SMEM_BUDGET // stage_bytes, max(per, 3)))
+                t = {"rows": 256, "TN": TN, "m_tiles": m_tiles, "n_tiles": ceil_div(N, 256),
+                     "splits": ceil_div(k_blocks, per), "stages": stages, "shared_bytes": stages * stage_bytes + 1024}
+                assert t["splits"] == 1 or t["splits"] * M * t["n_tiles"] * 256 * 4 <= TC_SCRATCH_BYTES
+            wide = t["rows"] == 256
+            self.launch(f"agi_gemm_tc_wide_{dtype}" if wide else f"agi_gemm_tc_{dtype}",
+                        (t["n_tiles"], t["m_tiles"], t["splits"]), (288 if wide else 160, 1, 1),
+                        tc_args + [U32(t["TN"]), U32(t["stages"])], shared_bytes=t["shared_bytes"], op=f"gemm_{dtype}",
+                        algorithm=f"tcgen05_{t['rows']}x{t['TN']}_s{t['stages']}_k{t['splits']}")
+            return
         t = tc_tiling(M, N, K, elem, splits)
         while t["splits"] > 1 and t["splits"] * M * t["n_tiles"] * 128 * 4 > TC_SCRATCH_BYTES:
             t = tc_tiling(M, N, K, elem, t["splits"] // 2)
-        partial, counters = self._tc_scratch
         assert t["tiles"] * 4 <= TC_COUNTER_BYTES
         self.launch(f"agi_gemm_tc_{dtype}", (t["n_tiles"], t["m_tiles"], t["splits"]), (160, 1, 1),
                     args[:7] + [partial, counters, Arena(STATUS_WORD)] + args[7:] + [U32(t["TN"]), U32(t["stages"])],

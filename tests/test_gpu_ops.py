@@ -242,6 +242,55 @@ def test_gemm_tcgen05(tmp_path, case):
     assert err < (1e-2 if dtype == "bf16" else 1e-2), err
 
 
+WIDE_CASES = [
+    (1024, 11008, 2048, "e4m3", 1, "plain"),        # prefill gate/up: 43 x 4 tiles of 256 x 256
+    (1024, 2048, 11008, "bf16", 4, "res"),          # prefill down projection, K in four slices
+    (288, 2560, 2048, "bf16", 1, "bias_gelu"),      # two token tiles of 144
+    (300, 1000, 512, "bf16", 2, "bias_res"),        # ragged: N, M not multiples of the tile; two slices
+    (130, 300, 256, "e4m3", 1, "bias"),             # second 128-row half mostly past N
+    (128, 256, 128, "bf16", 1, "plain"),            # one K block
+]
+
+
+@pytest.mark.parametrize("case", WIDE_CASES, ids=lambda c: "-".join(map(str, c)))
+def test_gemm_tcgen05_wide(tmp_path, case):
+    """256-row tensor-core kernel (two accumulators in tensor memory), direct and split-K epilogues."""
+    M, N, K, dtype, splits, epi = case
+    x, wf = randn(M, K, seed=41), randn(N, K, seed=42, std=0.02)
+    bias = randn(N, seed=43, std=0.1) if "bias" in epi else None
+    res = randn(M, N, seed=44) if "res" in epi else None
+    act = "gelu_tanh" if "gelu" in epi else None
+    weights, inputs = {}, {"x": x}
+    if dtype == "e4m3":
+        wq, ws = ops.quantize_e4m3(wf)
+        xq, xs = ops.quantize_e4m3(x)
+        weights.update({"w": wq, "w_scale": ws.reshape(())})
+        want = ops.gemm(xq, wq, bias=bias, residual=res, act=act, scale_a=xs, scale_w=ws)
+    else:
+        weights["w"] = wf.to(BF)
+        want = ops.gemm(x, wf.to(BF), bias=bias, residual=res, act=act)
+    if bias is not None:
+        weights["b"] = bias
+    if res is not None:
+        inputs["res"] = res
+
+    def body(r):
+        kw = dict(bias=Weight("b") if bias is not None else None, residual=Tensor("res") if res is not None else None,
+                  act=act, tactic="tcgen05_wide", splits=splits)
+        if dtype == "e4m3":
+            q, s = r.alloc(M * K), r.alloc(4)
+            r.quantize_e4m3(Tensor("x"), q, s, M * K)
+            r.gemm(q, Weight("w"), Tensor("y"), M, N, K, dtype="e4m3", scale_a=s, scale_w=Weight("w_scale"), **kw)
+        else:
+            r.gemm(Tensor("x"), Weight("w"), Tensor("y"), M, N, K, **kw)
+        r.export_status(Tensor("status"))
+
+    got, recipe = run_recipe(tmp_path, weights, inputs, {"y": (BF, (M, N)), "status": (torch.int32, (1,))}, body,
+                             repeats=3)
+    assert got["status"].item() == 0, hex(got["status"].item())
+    assert ops.max_rel_err(got["y"], want) < 1e-2
+
+
 SKINNY_CASES = [
     (17, 1536, 1536, "bf16", "bias_gelu_res"), (17, 6144, 1536, "bf16", "bias_gelu"), (17, 1536, 6144, "bf16", "bias_res"),
     (4, 3072, 1536, "bf16", "bias"), (1, 1024, 64, "bf16", "bias"), (16, 1536, 32, "bf16", "bias"),
