@@ -5,7 +5,7 @@
 Workload (``config.workload``): the GR00T-N1.5-shaped flow-matching DiT action head of the
 baseline's third configuration: 16 blocks x 1536, 17 tokens, cross-attention to 300 backbone
 tokens, 4 Euler steps, BF16 weights ~N(0, 0.02) seed 2, synthetic N(0, 1) inputs.  A "step" of
-this benchmark is one action chunk = one ``Session::Enqueue`` of the packaged recipe (599 kernel
+this benchmark is one action chunk = one ``Session::Enqueue`` of the packaged recipe (520 kernel
 launches replayed as one CUDA graph).  The real model's checkpoint is not available offline;
 seeded synthetic tensors of its shapes stand in.
 
@@ -122,22 +122,19 @@ def run_reference(args) -> None:
 
 def run_ours(args) -> None:
     import torch
-    import torch.distributed as dist
 
     from aginfer_b200.build import build_all
     from aginfer_b200.recipes import dit
     from aginfer_b200.recipes.package import build_aim
     from aginfer_b200.runner import Runner
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
+    from aginfer_b200.replicas import ReplicaGroup
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the recipe has no CPU execution path")
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    build_all()
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    group = ReplicaGroup.from_env("nccl")
+    world, rank, local = group.world, group.rank, group.local_rank
+    group.rank0_first(build_all)
 
     cfg = dit.DitConfig()
     weights, inputs = dit.synthetic_weights(cfg, seed=2), dit.synthetic_inputs(cfg, seed=2)
@@ -154,8 +151,7 @@ def run_ours(args) -> None:
 
     def barrier():
         torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
+        group.barrier()
         torch.cuda.synchronize()
 
     def timed(fn, iters: int) -> float:
@@ -183,12 +179,11 @@ def run_ours(args) -> None:
 
     if args.legs == "device":
         if rank == 0:
-            print(json.dumps({"metric": METRIC, "value": world * args.steps / (ms / 1000.0), "unit": UNIT,
+            print(json.dumps({"metric": METRIC, "value": group.whole_job_rate(args.steps, ms), "unit": UNIT,
                               "n_gpus": world, "steps": args.steps, "ms_per_step": ms / args.steps, "legs": "device"}))
         if sampler is not None:
             sampler.stop(t0, t1)
-        if world > 1:
-            dist.destroy_process_group()
+        group.close()
         tmp.cleanup()
         return
 
@@ -212,17 +207,14 @@ def run_ours(args) -> None:
     ms_e2e = timed(chunk_e2e, e2e_steps)
     clocks = sampler.stop(t0, t1) if sampler is not None else None
 
-    if world > 1:
-        both = torch.tensor([ms, ms_e2e], device="cuda")
-        dist.all_reduce(both, op=dist.ReduceOp.MAX)
-        ms, ms_e2e = both.tolist()
+    ms, ms_e2e = group.max_over_ranks([ms, ms_e2e])
     stats = runner.stats()
 
     result = None
     if rank == 0:
         peak, peak_kind = peaks()
         acc = dit.algorithmic_bytes(cfg)
-        value = world * args.steps / (ms / 1000.0)
+        value = group.whole_job_rate(args.steps, ms)
         result = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
@@ -234,7 +226,7 @@ def run_ours(args) -> None:
             "latency_ms_per_action_chunk": ms / args.steps,
             "chunk_weight_bytes": acc["per_chunk"],
             "chunk_hbm_frac_of_%s" % peak_kind: acc["per_chunk"] / (ms / args.steps / 1000.0) / 1e9 / peak,
-            "e2e": {"value": world * e2e_steps / (ms_e2e / 1000.0), "unit": UNIT, "h2d_bytes_per_step": h2d,
+            "e2e": {"value": group.whole_job_rate(e2e_steps, ms_e2e), "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / e2e_steps},
             "gpu_launches": int(stats["launches_per_enqueue"]) * args.steps,
             "launches_per_chunk": int(stats["launches_per_enqueue"]),
@@ -279,9 +271,7 @@ def run_ours(args) -> None:
             result["cpu_baseline"] = {"value": rate, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
                                       "sample": f"{chunks} whole action chunks of the same workload in {seconds:.1f} s"}
         print(json.dumps(result))
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    group.close()
     tmp.cleanup()
 
 
