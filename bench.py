@@ -267,7 +267,7 @@ def run_ours(args) -> None:
             "status_word": int(status.item()),
         }
         if world == 1 and not args.no_cpu_baseline:
-            rate, chunks, seconds = cpu_oracle_rate(cfg, weights, inputs, budget_s=15.0, max_chunks=10)
+            rate, chunks, seconds = cpu_oracle_rate(cfg, weights, inputs, budget_s=15.0, max_chunks=1000)
             result["cpu_baseline"] = {"value": rate, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
                                       "sample": f"{chunks} whole action chunks of the same workload in {seconds:.1f} s"}
         print(json.dumps(result))
