@@ -3,6 +3,7 @@
 #include "elementwise.cuh"
 #include "norm.cuh"
 #include "rope.cuh"
+#include "vision.cuh"
 #include "attention.cuh"
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"

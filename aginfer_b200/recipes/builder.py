@@ -220,14 +220,17 @@ class Profile:
 
 
 class RecipeBuilder:
-    def __init__(self, weights: Mapping[str, tuple[str, Sequence[int]]], arch: str = "sm100"):
+    def __init__(self, weights: Mapping[str, tuple[str, Sequence[int]]], arch: str = "sm100",
+                 counter_slots: int = (RESERVED - 64) // 4):
+        """``counter_slots``: u32 slots cleared by every run's first launch (one per dynamic quantisation)."""
         self.arch = arch
+        self.reserved = ceil_div(64 + 4 * counter_slots, ALIGN) * ALIGN
         self.weights = {k: (d, tuple(s)) for k, (d, s) in weights.items()}
         sizes = {k: math.prod(s) * CHECKPOINT_DTYPE_BYTES[d] for k, (d, s) in self.weights.items()}
         self.weight_offsets, self.weight_bytes = weight_layout(sizes)
         self.weight_sizes = sizes
-        self._cursor = RESERVED
-        self._high_water = RESERVED
+        self._cursor = self.reserved
+        self._high_water = self.reserved
         self._counter_cursor = 64          # counters live in [64, RESERVED); [0, 64) is the status area
         self.profiles: list[Profile] = []
         self.tactics: dict[tuple[str, str], dict[str, Any]] = {}
@@ -254,7 +257,7 @@ class RecipeBuilder:
         """A zero-at-run-start u32 slot (amax accumulators, flags)."""
         at = self._counter_cursor
         self._counter_cursor += 4 * words
-        if self._counter_cursor > RESERVED:
+        if self._counter_cursor > self.reserved:
             raise ValueError("out of per-run counter slots")
         return Arena(at)
 
@@ -268,7 +271,7 @@ class RecipeBuilder:
         self._profile = Profile(name, [dict(i) for i in inputs], [dict(o) for o in outputs], [], graph_safe)
         self.profiles.append(self._profile)
         # prologue: clear status word and counters
-        self.launch("agi_fill_u32", (1, 1, 1), (256, 1, 1), [Arena(0), U32(0), U32(RESERVED // 4)],
+        self.launch("agi_fill_u32", (1, 1, 1), (256, 1, 1), [Arena(0), U32(0), U32(self.reserved // 4)],
                     op="prologue", algorithm="fill_u32")
 
     def _encode(self, arg: Any) -> dict[str, Any]:
