@@ -191,8 +191,11 @@ def synthetic_inputs(cfg: VlConfig, seed: int = 3) -> dict:
             "positions": rope_positions(cfg)}
 
 
-def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto") -> RecipeBuilder:
-    """``weights``: name -> (dtype, shape) as from ``package.describe``."""
+def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto", trace: bool = False) -> RecipeBuilder:
+    """``weights``: name -> (dtype, shape) as from ``package.describe``.  ``trace`` adds three outputs for
+    block-by-block checks: ``vision_trace`` [v_layers + 1, patches, 1280] (the patch embedding, then every
+    block's output), ``merged_out`` [merged, hidden] (window order) and ``hidden_trace``
+    [layers + 1, tokens, hidden] (the assembled prefix, then every decoder layer's output)."""
     BF = 2
     P, VH, VD, VI = cfg.patches, cfg.v_hidden, cfg.v_head_dim, cfg.v_mlp_padded
     S, H, I, D = cfg.tokens, cfg.hidden, cfg.intermediate, cfg.head_dim
@@ -202,8 +205,19 @@ def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto") -> RecipeBui
                     [io("pixels", "F32", [cfg.images, cfg.channels, cfg.image_size, cfg.image_size]),
                      io("input_ids", "I32", [cfg.text_tokens]), io("positions", "I32", [3, S])],
                     [io("hidden_out", "BF16", [S, H]), io("kv_cache", "BF16", [cfg.layers, 2, S, cfg.kv_dim]),
-                     io("status", "I32", [1])])
+                     io("status", "I32", [1])] + ([io("vision_trace", "BF16", [cfg.v_layers + 1, P, VH]),
+                                                   io("merged_out", "BF16", [cfg.merged, H]),
+                                                   io("hidden_trace", "BF16", [cfg.layers + 1, S, H])] if trace else []))
     quant, scale = r.alloc(max(P * max(VH, VI), cfg.merged * cfg.merged_dim, S * max(H, I, cfg.q_dim))), r.alloc(4)
+
+    traces: list[tuple[object, str, int]] = []       # (arena buffer, output tensor, bytes): copied out at the end
+
+    def snapshot(src, name: str, index: int, nbytes: int) -> None:
+        """Keep a copy of ``src`` for output ``name``[index] (trace mode only)."""
+        if trace:
+            keep = r.alloc(nbytes)
+            r.launch("agi_copy_u32", (grid_for(nbytes // 4), 1, 1), (256, 1, 1), [src, keep, U32(nbytes // 4)], op="trace")
+            traces.append((keep, name, index, nbytes))
 
     def quantize(x, rows: int, K: int):
         r.quantize_e4m3(x, quant, scale, rows * K)
@@ -223,6 +237,7 @@ def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto") -> RecipeBui
              [Tensor("pixels"), patches, vpos, U32(cfg.images), U32(cfg.channels), U32(cfg.image_size), U32(cfg.patch),
               U32(cfg.temporal), U32(cfg.window), U32(cfg.merge), U32(cfg.patch_k), U32(cfg.patch_k)], op="patchify")
     r.gemm(patches, Weight("visual.patch_embed.proj.weight"), x, P, VH, cfg.patch_k, tactic=gemm_tactic)
+    snapshot(x, "vision_trace", 0, P * VH * BF)
     half = VD // 2
     for i in range(cfg.v_layers):
         b = f"visual.blocks.{i}"
@@ -244,6 +259,7 @@ def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto") -> RecipeBui
         r.swiglu(gate_up, gate_up + VI * BF, act, P, VI, 2 * VI)
         quantize(act, P, VI)
         linear_q(f"{b}.mlp.down_proj", x, P, VH, VI, residual=x2)
+        snapshot(x, "vision_trace", i + 1, P * VH * BF)
     # merger: per-patch norm; four consecutive rows of 1280 are one row of 5120
     M4, MD = cfg.merged, cfg.merged_dim
     mid, merged = r.alloc(M4 * MD * BF), r.alloc(M4 * H * BF)
@@ -252,6 +268,7 @@ def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto") -> RecipeBui
     linear_q("visual.merger.mlp.0", mid, M4, MD, MD, act="gelu_tanh")
     quantize(mid, M4, MD)
     linear_q("visual.merger.mlp.2", merged, M4, H, MD)
+    snapshot(merged, "merged_out", 0, M4 * H * BF)
 
     # ---------------- language model ----------------
     h, h2, hn = r.alloc(S * H * BF), r.alloc(S * H * BF), r.alloc(S * H * BF)
@@ -263,6 +280,7 @@ def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto") -> RecipeBui
     r.launch("agi_gather_rows_bf16", (grid_for(cfg.text_tokens * H // 8), 1, 1), (256, 1, 1),
              [Weight("model.embed_tokens.weight"), Tensor("input_ids"), h + M4 * H * BF, U32(cfg.text_tokens), U32(H),
               U32(cfg.vocab), U32(H)], op="embedding_gather")
+    snapshot(h, "hidden_trace", 0, S * H * BF)
     for i in range(cfg.layers):
         l = f"model.layers.{i}"
         k_cache = cache + (2 * i) * S * cfg.kv_dim * BF
@@ -286,11 +304,25 @@ def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto") -> RecipeBui
         r.swiglu(gu, gu + I * BF, sw, S, I, 2 * I)
         quantize(sw, S, I)
         linear_q(f"{l}.mlp.down_proj", h, S, H, I, residual=h2)
+        snapshot(h, "hidden_trace", i + 1, S * H * BF)
     r.rmsnorm(h, Weight("model.norm.weight"), Tensor("hidden_out"), S, H, cfg.eps)
     words = cfg.layers * 2 * S * cfg.kv_dim * BF // 4
     r.launch("agi_copy_u32", (grid_for(words), 1, 1), (256, 1, 1), [cache, Tensor("kv_cache"), U32(words)],
              op="export_kv_cache")
     r.export_status(Tensor("status"))
+    # trace outputs are whole tensors: gather the kept copies of one output into a contiguous run, copy once
+    for name in ("vision_trace", "merged_out", "hidden_trace"):
+        parts = sorted((t for t in traces if t[1] == name), key=lambda t: t[2])
+        if parts:
+            total = sum(t[3] for t in parts)
+            run = r.alloc(total)
+            at = 0
+            for keep, _, _, nbytes in parts:
+                r.launch("agi_copy_u32", (grid_for(nbytes // 4), 1, 1), (256, 1, 1), [keep, run + at, U32(nbytes // 4)],
+                         op="trace")
+                at += nbytes
+            r.launch("agi_copy_u32", (grid_for(total // 4), 1, 1), (256, 1, 1), [run, Tensor(name), U32(total // 4)],
+                     op="trace")
     return r
 
 

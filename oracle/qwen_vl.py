@@ -62,28 +62,29 @@ def _fp8_linear(w: dict, name: str, xq, xs, **kw) -> torch.Tensor:
                     **kw)
 
 
-def vision_tower(cfg, w: dict, pixels: torch.Tensor, layers: int | None = None) -> torch.Tensor:
-    """Merged image tokens [images * G * G, hidden] in window order."""
-    P, VH, VD, VI = cfg.patches, cfg.v_hidden, cfg.v_head_dim, cfg.v_mlp_padded
-    patches, pos = patchify(cfg, pixels)
-    x = ops.gemm(patches, w["visual.patch_embed.proj.weight"])
+def vision_block(cfg, w: dict, i: int, x: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+    """Block i of the vision tower over patch tokens x [patches, 1280] in window order."""
+    P, VH, VD = cfg.patches, cfg.v_hidden, cfg.v_head_dim
     half = VD // 2
     sections = (half // 2, half - half // 2, 0)
-    for i in range(cfg.v_layers if layers is None else layers):
-        b = f"visual.blocks.{i}"
-        xq, xs = ops.quantize_e4m3(ops.rmsnorm(x, w[f"{b}.norm1.weight"], cfg.eps))
-        qkv = _fp8_linear(w, f"{b}.attn.qkv", xq, xs)
-        qk = ops.mrope(qkv[:, :2 * VH].reshape(P, 2 * cfg.v_heads, VD), pos, cfg.v_theta, sections)
-        q, k = qk[:, :cfg.v_heads], qk[:, cfg.v_heads:]
-        v = qkv[:, 2 * VH:].reshape(P, cfg.v_heads, VD)
-        span = cfg.grid * cfg.grid if i in cfg.v_full_layers else cfg.window * cfg.window
-        att = ops.attention(q, k, v, mask="block", mask_arg=span).reshape(P, VH)
-        aq, as_ = ops.quantize_e4m3(att)
-        x2 = _fp8_linear(w, f"{b}.attn.proj", aq, as_, residual=x)
-        xq, xs = ops.quantize_e4m3(ops.rmsnorm(x2, w[f"{b}.norm2.weight"], cfg.eps))
-        act = ops.swiglu(_fp8_linear(w, f"{b}.mlp.gate_proj", xq, xs), _fp8_linear(w, f"{b}.mlp.up_proj", xq, xs))
-        aq, as_ = ops.quantize_e4m3(act)
-        x = _fp8_linear(w, f"{b}.mlp.down_proj", aq, as_, residual=x2)
+    b = f"visual.blocks.{i}"
+    xq, xs = ops.quantize_e4m3(ops.rmsnorm(x, w[f"{b}.norm1.weight"], cfg.eps))
+    qkv = _fp8_linear(w, f"{b}.attn.qkv", xq, xs)
+    qk = ops.mrope(qkv[:, :2 * VH].reshape(P, 2 * cfg.v_heads, VD), pos, cfg.v_theta, sections)
+    q, k = qk[:, :cfg.v_heads], qk[:, cfg.v_heads:]
+    v = qkv[:, 2 * VH:].reshape(P, cfg.v_heads, VD)
+    span = cfg.grid * cfg.grid if i in cfg.v_full_layers else cfg.window * cfg.window
+    att = ops.attention(q, k, v, mask="block", mask_arg=span).reshape(P, VH)
+    aq, as_ = ops.quantize_e4m3(att)
+    x2 = _fp8_linear(w, f"{b}.attn.proj", aq, as_, residual=x)
+    xq, xs = ops.quantize_e4m3(ops.rmsnorm(x2, w[f"{b}.norm2.weight"], cfg.eps))
+    act = ops.swiglu(_fp8_linear(w, f"{b}.mlp.gate_proj", xq, xs), _fp8_linear(w, f"{b}.mlp.up_proj", xq, xs))
+    aq, as_ = ops.quantize_e4m3(act)
+    return _fp8_linear(w, f"{b}.mlp.down_proj", aq, as_, residual=x2)
+
+
+def merger(cfg, w: dict, x: torch.Tensor) -> torch.Tensor:
+    """Patch tokens [patches, 1280] (window order) -> merged tokens [patches / 4, hidden] (window order)."""
     normed = ops.rmsnorm(x, w["visual.merger.ln_q.weight"], cfg.eps).reshape(cfg.merged, cfg.merged_dim)
     xq, xs = ops.quantize_e4m3(normed)
     mid = _fp8_linear(w, "visual.merger.mlp.0", xq, xs, act="gelu_tanh")
@@ -91,25 +92,38 @@ def vision_tower(cfg, w: dict, pixels: torch.Tensor, layers: int | None = None) 
     return _fp8_linear(w, "visual.merger.mlp.2", xq, xs)
 
 
+def vision_tower(cfg, w: dict, pixels: torch.Tensor) -> torch.Tensor:
+    """Merged image tokens [images * G * G, hidden] in window order."""
+    patches, pos = patchify(cfg, pixels)
+    x = ops.gemm(patches, w["visual.patch_embed.proj.weight"])
+    for i in range(cfg.v_layers):
+        x = vision_block(cfg, w, i, x, pos)
+    return merger(cfg, w, x)
+
+
+def decoder_layer(cfg, w: dict, i: int, h: torch.Tensor, positions: torch.Tensor):
+    """Layer i of the language model: (next hidden states, rotated K [tokens, kv_dim], V [tokens, kv_dim])."""
+    S, D = cfg.tokens, cfg.head_dim
+    l = f"model.layers.{i}"
+    xq, xs = ops.quantize_e4m3(ops.rmsnorm(h, w[f"{l}.input_layernorm.weight"], cfg.eps))
+    q = _fp8_linear(w, f"{l}.self_attn.q_proj", xq, xs).view(S, cfg.heads, D)
+    k = _fp8_linear(w, f"{l}.self_attn.k_proj", xq, xs).view(S, cfg.kv_heads, D)
+    v = _fp8_linear(w, f"{l}.self_attn.v_proj", xq, xs).view(S, cfg.kv_heads, D)
+    q, k = ops.mrope(q, positions, cfg.theta, cfg.sections), ops.mrope(k, positions, cfg.theta, cfg.sections)
+    att = ops.attention(q, k, v, mask="causal").reshape(S, cfg.q_dim)
+    aq, as_ = ops.quantize_e4m3(att)
+    h2 = _fp8_linear(w, f"{l}.self_attn.o_proj", aq, as_, residual=h)
+    xq, xs = ops.quantize_e4m3(ops.rmsnorm(h2, w[f"{l}.post_attention_layernorm.weight"], cfg.eps))
+    act = ops.swiglu(_fp8_linear(w, f"{l}.mlp.gate_proj", xq, xs), _fp8_linear(w, f"{l}.mlp.up_proj", xq, xs))
+    aq, as_ = ops.quantize_e4m3(act)
+    return _fp8_linear(w, f"{l}.mlp.down_proj", aq, as_, residual=h2), k.reshape(S, cfg.kv_dim), v.reshape(S, cfg.kv_dim)
+
+
 def language_model(cfg, w: dict, h: torch.Tensor, positions: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     """Hidden states [tokens, hidden] -> (final-norm hidden states, K/V cache [layers, 2, tokens, kv_dim])."""
-    S, D = cfg.tokens, cfg.head_dim
-    cache = torch.empty(cfg.layers, 2, S, cfg.kv_dim, dtype=torch.bfloat16)
+    cache = torch.empty(cfg.layers, 2, cfg.tokens, cfg.kv_dim, dtype=torch.bfloat16)
     for i in range(cfg.layers):
-        l = f"model.layers.{i}"
-        xq, xs = ops.quantize_e4m3(ops.rmsnorm(h, w[f"{l}.input_layernorm.weight"], cfg.eps))
-        q = _fp8_linear(w, f"{l}.self_attn.q_proj", xq, xs).view(S, cfg.heads, D)
-        k = _fp8_linear(w, f"{l}.self_attn.k_proj", xq, xs).view(S, cfg.kv_heads, D)
-        v = _fp8_linear(w, f"{l}.self_attn.v_proj", xq, xs).view(S, cfg.kv_heads, D)
-        q, k = ops.mrope(q, positions, cfg.theta, cfg.sections), ops.mrope(k, positions, cfg.theta, cfg.sections)
-        cache[i, 0], cache[i, 1] = k.reshape(S, cfg.kv_dim), v.reshape(S, cfg.kv_dim)
-        att = ops.attention(q, k, v, mask="causal").reshape(S, cfg.q_dim)
-        aq, as_ = ops.quantize_e4m3(att)
-        h2 = _fp8_linear(w, f"{l}.self_attn.o_proj", aq, as_, residual=h)
-        xq, xs = ops.quantize_e4m3(ops.rmsnorm(h2, w[f"{l}.post_attention_layernorm.weight"], cfg.eps))
-        act = ops.swiglu(_fp8_linear(w, f"{l}.mlp.gate_proj", xq, xs), _fp8_linear(w, f"{l}.mlp.up_proj", xq, xs))
-        aq, as_ = ops.quantize_e4m3(act)
-        h = _fp8_linear(w, f"{l}.mlp.down_proj", aq, as_, residual=h2)
+        h, cache[i, 0], cache[i, 1] = decoder_layer(cfg, w, i, h, positions)
     return ops.rmsnorm(h, w["model.norm.weight"], cfg.eps), cache
 
 
