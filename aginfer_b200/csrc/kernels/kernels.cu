@@ -5,6 +5,7 @@
 #include "rope.cuh"
 #include "vision.cuh"
 #include "attention.cuh"
+#include "attention_fa.cuh"
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
 #include "gemm_tc_wide.cuh"

@@ -151,6 +151,9 @@ def tc_prefill_plan(M: int, N: int, K: int, elem: int) -> dict[str, int]:
     return best
 
 
+FA_HEAD_DIMS = (48, 64, 80, 128)   # compiled widths of agi_attention_fa_bf16_d*
+
+
 TC_CLUSTER_SIZES = {"bf16": (2, 3, 4, 6, 8), "e4m3": (2, 4, 8)}   # compiled cluster variants
 
 
@@ -372,6 +375,12 @@ class RecipeBuilder:
             # few query rows: one block per head, tensor-core scores and P.V
             self.launch("agi_attention_mma_bf16", (q_heads, ceil_div(q_rows, 16), 1), (256, 1, 1), args, shared_bytes=mma_smem,
                         op=f"attention_{mask}", algorithm="mma_key_split")
+            return
+        if (aligned and head_dim in FA_HEAD_DIMS and q_stride % 2 == 0 and o_stride % 2 == 0
+                and algorithm in ("auto", "fa")):
+            # many query rows: streaming softmax on tensor cores, 64 rows per block, keys in tiles of 64
+            self.launch(f"agi_attention_fa_bf16_d{head_dim}", (ceil_div(q_rows, 64), q_heads, 1), (128, 1, 1), args,
+                        shared_bytes=4 * 64 * (head_dim + 8) * 2, op=f"attention_{mask}", algorithm="mma_streaming")
             return
         if (aligned and q_rows <= 32 and head_dim <= 64 and rows_smem <= ATTN_SMEM_BUDGET
                 and algorithm in ("auto", "key_split")):

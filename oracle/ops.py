@@ -129,6 +129,23 @@ def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return bf16_round(g * torch.sigmoid(g) * up.float())
 
 
+# Block-level tolerance for stacks whose GEMM inputs are quantised per tensor on the fly (scale = amax / 448).
+# A last-bit change of the largest activation moves the scale of the whole tensor, and with it the E4M3 code of
+# several percent of its elements, so two correct implementations that differ in one bf16 rounding upstream
+# differ by 3-4% of the output range after one block (measured on the oracle itself: see
+# tests/test_qwen_vl_cpu.py).  Kernels fed identical inputs are held to 1e-2; BF16 blocks to 2e-2.
+FP8_BLOCK_TOL = 5e-2
+
+
+def ulp_noise(x: torch.Tensor, frac: float, seed: int) -> torch.Tensor:
+    """Move a fraction ``frac`` of the bf16 elements of ``x`` by one unit in the last place, up or down."""
+    g = torch.Generator().manual_seed(seed)
+    bits = x.contiguous().view(torch.int16).clone()
+    pick = (torch.rand(x.shape, generator=g) < frac).to(torch.int16)
+    sign = torch.randint(0, 2, x.shape, generator=g).to(torch.int16) * 2 - 1
+    return (bits + pick * sign).view(torch.bfloat16)
+
+
 def max_rel_err(got: torch.Tensor, want: torch.Tensor) -> float:
     """max |got - want| / max |want|: the relative-error measure the parity tests use."""
     got, want = got.float(), want.float()

@@ -101,8 +101,9 @@ def vision_tower(cfg, w: dict, pixels: torch.Tensor) -> torch.Tensor:
     return merger(cfg, w, x)
 
 
-def decoder_layer(cfg, w: dict, i: int, h: torch.Tensor, positions: torch.Tensor):
-    """Layer i of the language model: (next hidden states, rotated K [tokens, kv_dim], V [tokens, kv_dim])."""
+def decoder_layer(cfg, w: dict, i: int, h: torch.Tensor, positions: torch.Tensor, attn_hook=None):
+    """Layer i of the language model: (next hidden states, rotated K [tokens, kv_dim], V [tokens, kv_dim]).
+    ``attn_hook`` (tests only) maps the attention output before it is quantised, e.g. to add last-bit noise."""
     S, D = cfg.tokens, cfg.head_dim
     l = f"model.layers.{i}"
     xq, xs = ops.quantize_e4m3(ops.rmsnorm(h, w[f"{l}.input_layernorm.weight"], cfg.eps))
@@ -111,6 +112,8 @@ def decoder_layer(cfg, w: dict, i: int, h: torch.Tensor, positions: torch.Tensor
     v = _fp8_linear(w, f"{l}.self_attn.v_proj", xq, xs).view(S, cfg.kv_heads, D)
     q, k = ops.mrope(q, positions, cfg.theta, cfg.sections), ops.mrope(k, positions, cfg.theta, cfg.sections)
     att = ops.attention(q, k, v, mask="causal").reshape(S, cfg.q_dim)
+    if attn_hook is not None:
+        att = attn_hook(att)
     aq, as_ = ops.quantize_e4m3(att)
     h2 = _fp8_linear(w, f"{l}.self_attn.o_proj", aq, as_, residual=h)
     xq, xs = ops.quantize_e4m3(ops.rmsnorm(h2, w[f"{l}.post_attention_layernorm.weight"], cfg.eps))

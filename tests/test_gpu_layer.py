@@ -33,7 +33,9 @@ def test_decoder_layer_matches_oracle(tmp_path, fp8):
     want = oracle_layer.forward(cfg, w, x)
     err, cos = ops.max_rel_err(got, want), ops.cosine(got, want)
     print(f"decoder layer fp8={fp8}: max_rel_err={err:.3e} cosine={cos:.6f} launches={stats['launches_per_enqueue']}")
-    assert err < 2e-2 and cos > 0.999
+    # BF16: 2e-2.  FP8: four per-tensor dynamic quantisations in the block put the oracle's own resolution at
+    # 3-4% of the output range (ops.FP8_BLOCK_TOL)
+    assert err < (ops.FP8_BLOCK_TOL if fp8 else 2e-2) and cos > 0.999
 
 
 def test_small_ragged_layer_with_the_audit_gemm(tmp_path):

@@ -148,6 +148,29 @@ def test_attention(tmp_path, case, algorithm):
     assert ops.max_rel_err(got["o"], want.reshape(sq, -1)) < MAX_REL
 
 
+FA_CASES = [
+    (288, 288, 16, 2, 128, "causal", 0),     # decoder prefill: grouped-query, 4.5 key tiles
+    (512, 512, 16, 16, 80, "block", 64),     # vision windows
+    (512, 512, 16, 16, 80, "block", 256),    # vision full-attention layers: one block per image
+    (100, 300, 4, 4, 64, "none", 0),         # cross attention, ragged both ways
+    (70, 130, 6, 3, 48, "causal", 60),       # queries are the last 70 of 130 positions
+    (17, 300, 32, 32, 48, "none", 0),        # fewer rows than one block
+    (200, 200, 2, 1, 128, "block", 24),      # blocks that straddle key tiles and row blocks
+]
+
+
+@pytest.mark.parametrize("case", FA_CASES, ids=lambda c: "x".join(map(str, c)))
+def test_attention_streaming_mma(tmp_path, case):
+    sq, skv, hq, hkv, d, mask, arg = case
+    q, k, v = randn(sq, hq * d, seed=9), randn(skv, hkv * d, seed=10), randn(skv, hkv * d, seed=11)
+    got, _ = run_recipe(tmp_path, {}, {"q": q, "k": k, "v": v}, {"o": (BF, (sq, hq * d))}, lambda r: r.attention(
+        Tensor("q"), Tensor("k"), Tensor("v"), Tensor("o"), q_rows=sq, kv_rows=skv, q_heads=hq, kv_heads=hkv,
+        head_dim=d, q_stride=hq * d, k_stride=hkv * d, v_stride=hkv * d, o_stride=hq * d, mask=mask, mask_arg=arg,
+        algorithm="fa"))
+    want = ops.attention(q.view(sq, hq, d), k.view(skv, hkv, d), v.view(skv, hkv, d), mask=mask, mask_arg=arg)
+    assert ops.max_rel_err(got["o"], want.reshape(sq, -1)) < MAX_REL
+
+
 def test_swiglu(tmp_path):
     rows, inter = 33, 11008
     gu = randn(rows, 2 * inter, seed=12)

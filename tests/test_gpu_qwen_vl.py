@@ -52,10 +52,11 @@ def test_reduced_depth_prefill_matches_oracle_block_by_block(tmp_path):
     """Real widths and token counts; 4 vision blocks (the last with full attention) and 4 decoder layers.
 
     Every GEMM input is quantised per tensor with a scale taken from the tensor's largest element, so a
-    last-bit difference in one activation moves the scale of a whole tensor and the next layer sees a
-    different E4M3 grid: the end-to-end comparison of a deep FP8 stack is loose by construction.  The parity
-    claim is therefore made block by block: each block's output on the GPU against the oracle's block fed
-    with the GPU's own input (max |diff| / max |ref| <= 2e-2), plus a cosine bound on the final states."""
+    last-bit difference in one activation moves the scale of a whole tensor and the next GEMM sees a
+    different E4M3 grid.  The parity claim is therefore made block by block: each block's output on the GPU
+    against the oracle's block fed with the GPU's own input, at ops.FP8_BLOCK_TOL (the oracle's own
+    resolution under one-ulp disturbances, measured in tests/test_qwen_vl_cpu.py); K/V, patch embedding,
+    merger and final norm, which have at most one quantisation upstream, at 2e-2; indexing bit-exact."""
     cfg = qwen_vl.VlConfig(v_layers=4, v_full_layers=(3,), layers=4, vocab=4096)
     w, x = qwen_vl.synthetic_weights(cfg), qwen_vl.synthetic_inputs(cfg)
     got, stats = run_prefill(tmp_path, cfg, w, x, trace=True)
@@ -73,7 +74,8 @@ def test_reduced_depth_prefill_matches_oracle_block_by_block(tmp_path):
         errs[f"kv_{i}"] = max(ops.max_rel_err(got["kv_cache"][i, 0], want_k), ops.max_rel_err(got["kv_cache"][i, 1], want_v))
     errs["final_norm"] = ops.max_rel_err(got["hidden_out"], ops.rmsnorm(ht[-1], w["model.norm.weight"], cfg.eps))
     print("teacher-forced block errors:", {k: round(v, 5) for k, v in errs.items()})
-    assert max(errs.values()) < 2e-2, errs
+    for name, err in errs.items():
+        assert err < (ops.FP8_BLOCK_TOL if name.startswith(("vision_block", "decoder_layer")) else 2e-2), (name, errs)
     want_hidden, _ = oracle_vl.forward(cfg, w, x["pixels"], x["input_ids"], x["positions"])
     cos = ops.cosine(got["hidden_out"], want_hidden)
     print(f"end to end: cosine={cos:.5f} max_rel_err={ops.max_rel_err(got['hidden_out'], want_hidden):.3e} "
