@@ -70,20 +70,42 @@ extern "C" __global__ void agi_quantize_e4m3_bf16(const bf16* x, uint8_t* q, con
     q[i] = float_to_e4m3(__fdiv_rn(__bfloat162float(x[i]), scale));
 }
 
-// out[r, c] = silu(gate[r, c]) * up[r, c]; gate/up may be column blocks of one wider buffer.
-extern "C" __global__ void agi_swiglu_bf16(const bf16* gate, const bf16* up, bf16* out, unsigned rows, unsigned cols,
-                                            unsigned in_stride, unsigned out_stride) {
+// out[r, c] = silu(gate[r, c]) * up[r, c]; gate/up may be column blocks of one wider buffer.  With kAmax the
+// maximum |out| (of the rounded values) is folded into *amax_bits for the dynamic quantisation that follows.
+template <bool kAmax>
+__device__ __forceinline__ void swiglu_body(const bf16* gate, const bf16* up, bf16* out, unsigned rows, unsigned cols,
+                                            unsigned in_stride, unsigned out_stride, unsigned* amax_bits) {
+  __shared__ float scratch[32];
   grid_dependency_wait();
   const unsigned per_row = cols / 8;
+  float best = 0.f;
   for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < rows * per_row; i += gridDim.x * blockDim.x) {
     const unsigned r = i / per_row, c = (i % per_row) * 8;
     float g[8], u[8];
     unpack8(*reinterpret_cast<const Bf16x8*>(gate + size_t(r) * in_stride + c), g);
     unpack8(*reinterpret_cast<const Bf16x8*>(up + size_t(r) * in_stride + c), u);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) g[j] = silu(g[j]) * u[j];
+    for (int j = 0; j < 8; ++j) {
+      g[j] = silu(g[j]) * u[j];
+      if (kAmax) best = fmaxf(best, fabsf(g[j]));
+    }
     *reinterpret_cast<Bf16x8*>(out + size_t(r) * out_stride + c) = pack8(g);
   }
+  if (kAmax) {
+    best = block_max(best, scratch);
+    if (threadIdx.x == 0) atomicMax(amax_bits, __float_as_uint(__bfloat162float(__float2bfloat16_rn(best))));
+  }
+}
+
+extern "C" __global__ void agi_swiglu_bf16(const bf16* gate, const bf16* up, bf16* out, unsigned rows, unsigned cols,
+                                            unsigned in_stride, unsigned out_stride) {
+  swiglu_body<false>(gate, up, out, rows, cols, in_stride, out_stride, nullptr);
+}
+
+extern "C" __global__ void agi_swiglu_amax_bf16(const bf16* gate, const bf16* up, bf16* out, unsigned rows,
+                                                 unsigned cols, unsigned in_stride, unsigned out_stride,
+                                                 unsigned* amax_bits) {
+  swiglu_body<true>(gate, up, out, rows, cols, in_stride, out_stride, amax_bits);
 }
 
 // Flow-matching Euler update on the fp32 action latent: x += dt * v (v is the bf16 velocity);

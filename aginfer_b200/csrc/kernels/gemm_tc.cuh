@@ -562,6 +562,33 @@ agi_gemm_tc_bf16_x16(const bf16* x, void* y, unsigned* status, unsigned M, unsig
                        M, N, K, ldx, ldy, flags, TN, stages, blockIdx.x % tiles);
 }
 
+// Up to three GEMMs over the same activation matrix as ONE launch (Q | K | V, gate | up): part i multiplies
+// by w_i [N_i, K], scales by scale_a * sw_i, adds bias_i and writes y_i with row pitch ldy_i.  The parts'
+// 128-row tiles are laid end to end along grid.x = sum of ceil(N_i / 128); no split-K.
+#define AGI_TC_GROUP_KERNEL(NAME, TYPE, FP8)                                                                          \
+  extern "C" __global__ void __launch_bounds__(tc::kThreads, 1)                                                      \
+  NAME(const TYPE* x, const float* scale_a, unsigned* status, unsigned M, unsigned K, unsigned ldx, unsigned flags,   \
+       unsigned TN, unsigned stages, const TYPE* w0, const bf16* bias0, const float* sw0, void* y0, unsigned N0,      \
+       unsigned ldy0, const TYPE* w1, const bf16* bias1, const float* sw1, void* y1, unsigned N1, unsigned ldy1,      \
+       const TYPE* w2, const bf16* bias2, const float* sw2, void* y2, unsigned N2, unsigned ldy2) {                   \
+    const unsigned t0 = (N0 + tc::kTileN - 1) / tc::kTileN, t1 = (N1 + tc::kTileN - 1) / tc::kTileN;                  \
+    const TYPE* w = w0;                                                                                               \
+    const bf16* bias = bias0;                                                                                         \
+    const float* sw = sw0;                                                                                            \
+    void* y = y0;                                                                                                     \
+    unsigned N = N0, ldy = ldy0, tile = blockIdx.x;                                                                   \
+    if (tile >= t0 + t1) {                                                                                            \
+      w = w2; bias = bias2; sw = sw2; y = y2; N = N2; ldy = ldy2; tile -= t0 + t1;                                    \
+    } else if (tile >= t0) {                                                                                          \
+      w = w1; bias = bias1; sw = sw1; y = y1; N = N1; ldy = ldy1; tile -= t0;                                         \
+    }                                                                                                                 \
+    tc::gemm_body<FP8>(reinterpret_cast<const uint8_t*>(x), reinterpret_cast<const uint8_t*>(w), y, bias, bias,      \
+                       scale_a, sw, nullptr, nullptr, status, M, N, K, ldx, ldy, flags, TN, stages, tile);            \
+  }
+AGI_TC_GROUP_KERNEL(agi_gemm_tc_bf16_x3, bf16, false)
+AGI_TC_GROUP_KERNEL(agi_gemm_tc_e4m3_x3, uint8_t, true)
+#undef AGI_TC_GROUP_KERNEL
+
 extern "C" __global__ void __launch_bounds__(tc::kThreads, 1)
 agi_gemm_tc_bf16(const bf16* x, const bf16* w, void* y, const bf16* bias, const bf16* residual, const float* scale_a,
                  const float* scale_w, float* partial, unsigned* counters, unsigned* status, unsigned M, unsigned N,

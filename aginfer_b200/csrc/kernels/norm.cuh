@@ -4,10 +4,13 @@
 
 #include "common.cuh"
 
-// One block per row, `cols` a multiple of 8.  y = bf16(x * rsqrt(mean(x^2) + eps) * gain).
-extern "C" __global__ void agi_rmsnorm_bf16(const bf16* x, const bf16* gain, bf16* y, unsigned rows, unsigned cols,
-                                             unsigned x_stride, unsigned y_stride, float eps) {
-  AGI_TRACE_KERNEL(2);
+// One block per row, `cols` a multiple of 8.  y = bf16(x * rsqrt(mean(x^2) + eps) * gain).  With kAmax the
+// kernel also folds max |y| (of the rounded outputs) into *amax_bits, which saves the separate pass of the
+// dynamic quantisation that follows (rounding is monotonic, so the rounded maximum is the maximum of the
+// rounded values).
+template <bool kAmax>
+__device__ __forceinline__ void rmsnorm_body(const bf16* x, const bf16* gain, bf16* y, unsigned rows, unsigned cols,
+                                             unsigned x_stride, unsigned y_stride, float eps, unsigned* amax_bits) {
   __shared__ float scratch[32];
   grid_dependency_wait();
   const unsigned row = blockIdx.x;
@@ -24,14 +27,34 @@ extern "C" __global__ void agi_rmsnorm_bf16(const bf16* x, const bf16* gain, bf1
     for (int j = 0; j < 8; ++j) sumsq += f[j] * f[j];
   }
   const float rstd = rsqrtf(block_sum(sumsq, scratch) / float(cols) + eps);
+  float best = 0.f;
   for (unsigned i = threadIdx.x; i < vectors; i += blockDim.x) {
     float f[8], g[8];
     unpack8(xr[i], f);
     unpack8(gr[i], g);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) f[j] = f[j] * rstd * g[j];
+    for (int j = 0; j < 8; ++j) {
+      f[j] = f[j] * rstd * g[j];
+      if (kAmax) best = fmaxf(best, fabsf(f[j]));
+    }
     yr[i] = pack8(f);
   }
+  if (kAmax) {
+    __syncthreads();  // scratch is reused
+    best = block_max(best, scratch);
+    if (threadIdx.x == 0) atomicMax(amax_bits, __float_as_uint(__bfloat162float(__float2bfloat16_rn(best))));
+  }
+}
+
+extern "C" __global__ void agi_rmsnorm_bf16(const bf16* x, const bf16* gain, bf16* y, unsigned rows, unsigned cols,
+                                             unsigned x_stride, unsigned y_stride, float eps) {
+  AGI_TRACE_KERNEL(2);
+  rmsnorm_body<false>(x, gain, y, rows, cols, x_stride, y_stride, eps, nullptr);
+}
+
+extern "C" __global__ void agi_rmsnorm_amax_bf16(const bf16* x, const bf16* gain, bf16* y, unsigned rows, unsigned cols,
+                                                  unsigned x_stride, unsigned y_stride, float eps, unsigned* amax_bits) {
+  rmsnorm_body<true>(x, gain, y, rows, cols, x_stride, y_stride, eps, amax_bits);
 }
 
 // One block per row.  y = bf16(((x - mean) * rstd) * (1 + scale[c]) + shift[c]) when

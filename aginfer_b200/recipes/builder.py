@@ -151,6 +151,24 @@ def tc_prefill_plan(M: int, N: int, K: int, elem: int) -> dict[str, int]:
     return best
 
 
+def tc_group_tiling(M: int, n_tiles: int, K: int, elem: int) -> dict[str, int]:
+    """Token tile and ring depth of the grouped tensor-core GEMM (128-row tiles, no K slices): the token tile
+    with the cheapest estimate under the same model as ``tc_prefill_plan``."""
+    k_blocks = K * elem // 128
+    best: dict[str, int] | None = None
+    for cap in range(256, 15, -16):
+        m_tiles = ceil_div(M, cap)
+        TN = ceil_div(ceil_div(M, m_tiles), 16) * 16
+        stage_bytes = 16384 + TN * 128
+        cost = ceil_div(n_tiles * m_tiles, SM_COUNT) * (k_blocks * max(stage_bytes / 28, TN * 2) + 5000 + TN * 25)
+        if best is None or cost < best["cost"]:
+            stages = max(3, min(12, TC_SMEM_BUDGET // stage_bytes, max(k_blocks, 3)))
+            best = {"TN": TN, "m_tiles": m_tiles, "stages": stages, "shared_bytes": stages * stage_bytes + 1024,
+                    "cost": int(cost)}
+    assert best is not None
+    return best
+
+
 FA_HEAD_DIMS = (48, 64, 80, 128)   # compiled widths of agi_attention_fa_bf16_d*
 
 
@@ -312,20 +330,24 @@ class RecipeBuilder:
         self.launch("vector_add_f32", (ceil_div(count, 256), 1, 1), (256, 1, 1), [left, right, out, U32(count)],
                     op="vector_add")
 
-    def quantize_e4m3(self, x: Pointer, q: Pointer, scale_out: Pointer, count: int) -> None:
-        """amax -> scale = amax / 448 -> q = e4m3(x / scale); two launches sharing one counter."""
-        amax = self.counter()
+    def quantize_e4m3(self, x: Pointer, q: Pointer, scale_out: Pointer, count: int, amax: Pointer | None = None) -> None:
+        """amax -> scale = amax / 448 -> q = e4m3(x / scale); two launches sharing one counter, or one launch
+        when the producer of ``x`` already folded max |x| into ``amax`` (a ``counter()`` slot)."""
         blocks = grid_for(count // 8 + 1, 256, SM_COUNT * 4)
-        self.launch("agi_absmax_bf16", (blocks, 1, 1), (256, 1, 1), [x, U32(count), amax], op="absmax")
+        if amax is None:
+            amax = self.counter()
+            self.launch("agi_absmax_bf16", (blocks, 1, 1), (256, 1, 1), [x, U32(count), amax], op="absmax")
         self.launch("agi_quantize_e4m3_bf16", (blocks, 1, 1), (256, 1, 1), [x, q, amax, scale_out, U32(count)],
                     op="quantize_e4m3")
 
     def rmsnorm(self, x: Pointer, gain: Pointer, y: Pointer, rows: int, cols: int, eps: float = 1e-6,
-                x_stride: int | None = None, y_stride: int | None = None) -> None:
+                x_stride: int | None = None, y_stride: int | None = None, amax: Pointer | None = None) -> None:
+        """``amax``: a ``counter()`` slot that receives max |y| for a following ``quantize_e4m3(..., amax=)``."""
         assert cols % 8 == 0
-        self.launch("agi_rmsnorm_bf16", (rows, 1, 1), (min(1024, max(32, ceil_div(cols // 8, 32) * 32)), 1, 1),
-                    [x, gain, y, U32(rows), U32(cols), U32(x_stride or cols), U32(y_stride or cols), F32(eps)],
-                    op="rmsnorm")
+        args = [x, gain, y, U32(rows), U32(cols), U32(x_stride or cols), U32(y_stride or cols), F32(eps)]
+        self.launch("agi_rmsnorm_amax_bf16" if amax is not None else "agi_rmsnorm_bf16", (rows, 1, 1),
+                    (min(1024, max(32, ceil_div(cols // 8, 32) * 32)), 1, 1), args + ([amax] if amax is not None else []),
+                    op="rmsnorm_amax" if amax is not None else "rmsnorm")
 
     def layernorm(self, x: Pointer, y: Pointer, rows: int, cols: int, eps: float = 1e-5,
                   scale: Pointer | None = None, shift: Pointer | None = None,
@@ -396,10 +418,12 @@ class RecipeBuilder:
                     op=f"attention_{mask}", algorithm="warp_per_row")
 
     def swiglu(self, gate: Pointer, up: Pointer, out: Pointer, rows: int, cols: int, in_stride: int,
-               out_stride: int | None = None) -> None:
+               out_stride: int | None = None, amax: Pointer | None = None) -> None:
         assert cols % 8 == 0
-        self.launch("agi_swiglu_bf16", (grid_for(rows * cols // 8), 1, 1), (256, 1, 1),
-                    [gate, up, out, U32(rows), U32(cols), U32(in_stride), U32(out_stride or cols)], op="swiglu")
+        args = [gate, up, out, U32(rows), U32(cols), U32(in_stride), U32(out_stride or cols)]
+        self.launch("agi_swiglu_amax_bf16" if amax is not None else "agi_swiglu_bf16",
+                    (grid_for(rows * cols // 8), 1, 1), (256, 1, 1), args + ([amax] if amax is not None else []),
+                    op="swiglu_amax" if amax is not None else "swiglu")
 
     def gemm(self, x: Pointer, w: Pointer, y: Pointer, M: int, N: int, K: int, *, dtype: str = "bf16",
              bias: Pointer | None = None, residual: Pointer | None = None, act: str | None = None,
@@ -493,6 +517,35 @@ class RecipeBuilder:
                     args[:7] + [partial, counters, Arena(STATUS_WORD)] + args[7:] + [U32(t["TN"]), U32(t["stages"])],
                     shared_bytes=t["shared_bytes"], op=f"gemm_{dtype}",
                     algorithm=f"tcgen05_128x{t['TN']}_s{t['stages']}_k{t['splits']}")
+
+    def gemm_group(self, x: Pointer, parts: Sequence[tuple[Pointer, Pointer | None, Pointer | None, Pointer, int, int]],
+                   M: int, K: int, *, dtype: str = "bf16", scale_a: Pointer | None = None, ldx: int | None = None,
+                   act: str | None = None) -> None:
+        """Up to three GEMMs over one activation matrix in one tensor-core launch (Q | K | V, gate | up).
+        ``parts``: ``(weight, bias or None, weight scale or None, y, N, ldy)``; either every part has a bias
+        or none has; with ``scale_a`` every part brings its weight scale."""
+        assert 1 <= len(parts) <= 3
+        elem = 1 if dtype == "e4m3" else 2
+        if (K * elem) % 128 or ((ldx or K) * elem) % 16:
+            raise ValueError("grouped tcgen05 GEMM needs K bytes % 128 == 0 and 16-byte aligned rows")
+        has_bias = parts[0][1] is not None
+        assert all((p[1] is not None) == has_bias for p in parts)
+        assert all((p[2] is not None) == (scale_a is not None) for p in parts)
+        flags = ACT[act] | (FLAG_BIAS if has_bias else 0) | (FLAG_SCALED if scale_a else 0)
+        t = tc_group_tiling(M, sum(ceil_div(p[4], 128) for p in parts), K, elem)
+        dummy = Arena(0)
+        args: list[Any] = [x, scale_a or dummy, Arena(STATUS_WORD), U32(M), U32(K), U32(ldx or K), U32(flags),
+                           U32(t["TN"]), U32(t["stages"])]
+        for i in range(3):
+            if i < len(parts):
+                w, bias, sw, y, N, ldy = parts[i]
+                args += [w, bias or dummy, sw or dummy, y, U32(N), U32(ldy)]
+            else:
+                args += [dummy, dummy, dummy, dummy, U32(0), U32(0)]
+        grid_x = sum(ceil_div(p[4], 128) for p in parts)
+        self.launch(f"agi_gemm_tc_{dtype}_x3", (grid_x, t["m_tiles"], 1), (160, 1, 1), args,
+                    shared_bytes=t["shared_bytes"], op=f"gemm_{dtype}_group",
+                    algorithm=f"tcgen05_128x{t['TN']}_s{t['stages']}_x{len(parts)}")
 
     def gemm_batch(self, x: Pointer, parts: Sequence[tuple[Pointer, Pointer]], y: Pointer, M: int, N: int, K: int,
                    seg_stride: int, ldx: int | None = None) -> None:

@@ -191,11 +191,13 @@ def synthetic_inputs(cfg: VlConfig, seed: int = 3) -> dict:
             "positions": rope_positions(cfg)}
 
 
-def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto", trace: bool = False) -> RecipeBuilder:
+def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto", trace: bool = False,
+                 group: bool = True) -> RecipeBuilder:
     """``weights``: name -> (dtype, shape) as from ``package.describe``.  ``trace`` adds three outputs for
     block-by-block checks: ``vision_trace`` [v_layers + 1, patches, 1280] (the patch embedding, then every
     block's output), ``merged_out`` [merged, hidden] (window order) and ``hidden_trace``
-    [layers + 1, tokens, hidden] (the assembled prefix, then every decoder layer's output)."""
+    [layers + 1, tokens, hidden] (the assembled prefix, then every decoder layer's output).  ``group`` runs the
+    projections that share an input (Q | K | V, gate | up) as one launch each."""
     BF = 2
     P, VH, VD, VI = cfg.patches, cfg.v_hidden, cfg.v_head_dim, cfg.v_mlp_padded
     S, H, I, D = cfg.tokens, cfg.hidden, cfg.intermediate, cfg.head_dim
@@ -219,8 +221,29 @@ def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto", trace: bool 
             r.launch("agi_copy_u32", (grid_for(nbytes // 4), 1, 1), (256, 1, 1), [src, keep, U32(nbytes // 4)], op="trace")
             traces.append((keep, name, index, nbytes))
 
-    def quantize(x, rows: int, K: int):
-        r.quantize_e4m3(x, quant, scale, rows * K)
+    def quantize(x, rows: int, K: int, amax=None):
+        r.quantize_e4m3(x, quant, scale, rows * K, amax=amax)
+
+    def norm_quantize(x, gain: str, y, rows: int, cols: int, q_rows: int | None = None, q_cols: int | None = None):
+        """RMSNorm that also leaves max |y| behind, then the E4M3 quantisation of y (viewed [q_rows, q_cols])."""
+        amax = r.counter()
+        r.rmsnorm(x, Weight(gain), y, rows, cols, cfg.eps, amax=amax)
+        quantize(y, q_rows or rows, q_cols or cols, amax=amax)
+
+    def swiglu_quantize(gate, up, out, rows: int, cols: int):
+        amax = r.counter()
+        r.swiglu(gate, up, out, rows, cols, 2 * cols, amax=amax)
+        quantize(out, rows, cols, amax=amax)
+
+    def group_q(parts, M: int, K: int) -> None:
+        """``parts``: (name, y, N, ldy); FP8 GEMMs over ``quant`` sharing one launch when ``group`` is set."""
+        if group and gemm_tactic == "auto":
+            r.gemm_group(quant, [(Weight(f"{n}.weight"), Weight(f"{n}.bias") if f"{n}.bias" in weights else None,
+                                  Weight(f"{n}.weight_scale"), y, N, ldy) for n, y, N, ldy in parts], M, K,
+                         dtype="e4m3", scale_a=scale)
+        else:
+            for n, y, N, ldy in parts:
+                linear_q(n, y, M, N, K, ldy=ldy)
 
     def linear_q(name: str, y, M: int, N: int, K: int, **kw) -> None:
         """FP8 GEMM over the activations last quantised into ``quant``."""
@@ -241,8 +264,7 @@ def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto", trace: bool 
     half = VD // 2
     for i in range(cfg.v_layers):
         b = f"visual.blocks.{i}"
-        r.rmsnorm(x, Weight(f"{b}.norm1.weight"), normed, P, VH, cfg.eps)
-        quantize(normed, P, VH)
+        norm_quantize(x, f"{b}.norm1.weight", normed, P, VH)
         linear_q(f"{b}.attn.qkv", qkv, P, 3 * VH, VH)
         # rows x (q heads + k heads) of width 80 sit side by side at the start of each qkv row
         r.mrope(qkv, vpos, P, 2 * cfg.v_heads, VD, 3 * VH, cfg.v_theta, (half // 2, half - half // 2, 0))
@@ -252,19 +274,15 @@ def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto", trace: bool 
                     mask="block", mask_arg=span)
         quantize(attn, P, VH)
         linear_q(f"{b}.attn.proj", x2, P, VH, VH, residual=x)
-        r.rmsnorm(x2, Weight(f"{b}.norm2.weight"), normed, P, VH, cfg.eps)
-        quantize(normed, P, VH)
-        linear_q(f"{b}.mlp.gate_proj", gate_up, P, VI, VH, ldy=2 * VI)
-        linear_q(f"{b}.mlp.up_proj", gate_up + VI * BF, P, VI, VH, ldy=2 * VI)
-        r.swiglu(gate_up, gate_up + VI * BF, act, P, VI, 2 * VI)
-        quantize(act, P, VI)
+        norm_quantize(x2, f"{b}.norm2.weight", normed, P, VH)
+        group_q([(f"{b}.mlp.gate_proj", gate_up, VI, 2 * VI), (f"{b}.mlp.up_proj", gate_up + VI * BF, VI, 2 * VI)], P, VH)
+        swiglu_quantize(gate_up, gate_up + VI * BF, act, P, VI)
         linear_q(f"{b}.mlp.down_proj", x, P, VH, VI, residual=x2)
         snapshot(x, "vision_trace", i + 1, P * VH * BF)
     # merger: per-patch norm; four consecutive rows of 1280 are one row of 5120
     M4, MD = cfg.merged, cfg.merged_dim
     mid, merged = r.alloc(M4 * MD * BF), r.alloc(M4 * H * BF)
-    r.rmsnorm(x, Weight("visual.merger.ln_q.weight"), normed, P, VH, cfg.eps)
-    quantize(normed, M4, MD)
+    norm_quantize(x, "visual.merger.ln_q.weight", normed, P, VH, M4, MD)
     linear_q("visual.merger.mlp.0", mid, M4, MD, MD, act="gelu_tanh")
     quantize(mid, M4, MD)
     linear_q("visual.merger.mlp.2", merged, M4, H, MD)
@@ -285,11 +303,9 @@ def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto", trace: bool 
         l = f"model.layers.{i}"
         k_cache = cache + (2 * i) * S * cfg.kv_dim * BF
         v_cache = cache + (2 * i + 1) * S * cfg.kv_dim * BF
-        r.rmsnorm(h, Weight(f"{l}.input_layernorm.weight"), hn, S, H, cfg.eps)
-        quantize(hn, S, H)
-        linear_q(f"{l}.self_attn.q_proj", q_buf, S, cfg.q_dim, H)
-        linear_q(f"{l}.self_attn.k_proj", k_cache, S, cfg.kv_dim, H)
-        linear_q(f"{l}.self_attn.v_proj", v_cache, S, cfg.kv_dim, H)
+        norm_quantize(h, f"{l}.input_layernorm.weight", hn, S, H)
+        group_q([(f"{l}.self_attn.q_proj", q_buf, cfg.q_dim, cfg.q_dim), (f"{l}.self_attn.k_proj", k_cache, cfg.kv_dim,
+                  cfg.kv_dim), (f"{l}.self_attn.v_proj", v_cache, cfg.kv_dim, cfg.kv_dim)], S, H)
         r.mrope(q_buf, Tensor("positions"), S, cfg.heads, D, cfg.q_dim, cfg.theta, cfg.sections)
         r.mrope(k_cache, Tensor("positions"), S, cfg.kv_heads, D, cfg.kv_dim, cfg.theta, cfg.sections)
         r.attention(q_buf, k_cache, v_cache, att, q_rows=S, kv_rows=S, q_heads=cfg.heads, kv_heads=cfg.kv_heads,
@@ -297,12 +313,9 @@ def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto", trace: bool 
                     mask="causal")
         quantize(att, S, cfg.q_dim)
         linear_q(f"{l}.self_attn.o_proj", h2, S, H, cfg.q_dim, residual=h)
-        r.rmsnorm(h2, Weight(f"{l}.post_attention_layernorm.weight"), hn, S, H, cfg.eps)
-        quantize(hn, S, H)
-        linear_q(f"{l}.mlp.gate_proj", gu, S, I, H, ldy=2 * I)
-        linear_q(f"{l}.mlp.up_proj", gu + I * BF, S, I, H, ldy=2 * I)
-        r.swiglu(gu, gu + I * BF, sw, S, I, 2 * I)
-        quantize(sw, S, I)
+        norm_quantize(h2, f"{l}.post_attention_layernorm.weight", hn, S, H)
+        group_q([(f"{l}.mlp.gate_proj", gu, I, 2 * I), (f"{l}.mlp.up_proj", gu + I * BF, I, 2 * I)], S, H)
+        swiglu_quantize(gu, gu + I * BF, sw, S, I)
         linear_q(f"{l}.mlp.down_proj", h, S, H, I, residual=h2)
         snapshot(h, "hidden_trace", i + 1, S * H * BF)
     r.rmsnorm(h, Weight("model.norm.weight"), Tensor("hidden_out"), S, H, cfg.eps)

@@ -314,6 +314,72 @@ def test_gemm_tcgen05_wide(tmp_path, case):
     assert ops.max_rel_err(got["y"], want) < 1e-2
 
 
+@pytest.mark.parametrize("dtype,M,K,widths", [("e4m3", 288, 2048, (2048, 256, 256)), ("bf16", 300, 512, (1000, 72)),
+                                              ("e4m3", 512, 1280, (3456, 3456)), ("bf16", 17, 128, (128,))])
+def test_gemm_group(tmp_path, dtype, M, K, widths):
+    """Q | K | V style: several weight matrices over one activation matrix in one tensor-core launch."""
+    x = randn(M, K, seed=61)
+    weights, wants, outs = {}, [], {}
+    if dtype == "e4m3":
+        xq, xs = ops.quantize_e4m3(x)
+    for i, n in enumerate(widths):
+        wf, bias = randn(n, K, seed=62 + i, std=0.02), randn(n, seed=72 + i, std=0.1)
+        weights[f"b{i}"] = bias
+        if dtype == "e4m3":
+            wq, ws = ops.quantize_e4m3(wf)
+            weights[f"w{i}"], weights[f"s{i}"] = wq, ws.reshape(())
+            wants.append(ops.gemm(xq, wq, bias=bias, scale_a=xs, scale_w=ws))
+        else:
+            weights[f"w{i}"] = wf.to(BF)
+            wants.append(ops.gemm(x, wf.to(BF), bias=bias))
+        outs[f"y{i}"] = (BF, (M, n))
+
+    def body(r):
+        src, scale = Tensor("x"), None
+        if dtype == "e4m3":
+            src, scale = r.alloc(M * K), r.alloc(4)
+            r.quantize_e4m3(Tensor("x"), src, scale, M * K)
+        r.gemm_group(src, [(Weight(f"w{i}"), Weight(f"b{i}"), Weight(f"s{i}") if dtype == "e4m3" else None,
+                            Tensor(f"y{i}"), n, n) for i, n in enumerate(widths)], M, K, dtype=dtype, scale_a=scale)
+        r.export_status(Tensor("status"))
+
+    got, _ = run_recipe(tmp_path, weights, {"x": x}, {**outs, "status": (torch.int32, (1,))}, body, repeats=2)
+    assert got["status"].item() == 0
+    for i, want in enumerate(wants):
+        assert ops.max_rel_err(got[f"y{i}"], want) < 1e-2, i
+
+
+def test_producers_that_fold_the_amax_match_the_separate_pass(tmp_path):
+    """RMSNorm / SwiGLU variants that leave max |y| behind: the quantisation that follows must produce the same
+    bytes and the same scale as the two-pass form (bit-exact tier)."""
+    rows, cols = 288, 2048
+    x, gain = randn(rows, cols, seed=81), (1.0 + 0.1 * randn(cols, seed=82).float()).to(BF)
+    gu = randn(rows, 2 * cols, seed=83)
+
+    def body(r):
+        y1, y2, a, h1, h2 = (r.alloc(rows * cols * 2) for _ in range(5))
+        amax = r.counter()
+        r.rmsnorm(Tensor("x"), Weight("gain"), y1, rows, cols, 1e-6)
+        r.quantize_e4m3(y1, Tensor("q_two_pass"), Tensor("s_two_pass"), rows * cols)
+        r.rmsnorm(Tensor("x"), Weight("gain"), y2, rows, cols, 1e-6, amax=amax)
+        r.quantize_e4m3(y2, Tensor("q_folded"), Tensor("s_folded"), rows * cols, amax=amax)
+        amax2 = r.counter()
+        r.swiglu(Tensor("gu"), Tensor("gu"), h1, rows, cols, 2 * cols)
+        r.quantize_e4m3(h1, Tensor("g_two_pass"), Tensor("t_two_pass"), rows * cols)
+        r.swiglu(Tensor("gu"), Tensor("gu"), h2, rows, cols, 2 * cols, amax=amax2)
+        r.quantize_e4m3(h2, Tensor("g_folded"), Tensor("t_folded"), rows * cols, amax=amax2)
+
+    u8, f32 = (torch.uint8, (rows, cols)), (torch.float32, (1,))
+    got, _ = run_recipe(tmp_path, {"gain": gain}, {"x": x, "gu": gu},
+                        {"q_two_pass": u8, "s_two_pass": f32, "q_folded": u8, "s_folded": f32, "g_two_pass": u8,
+                         "t_two_pass": f32, "g_folded": u8, "t_folded": f32}, body, repeats=2)
+    assert torch.equal(got["s_two_pass"], got["s_folded"]) and torch.equal(got["q_two_pass"], got["q_folded"])
+    assert torch.equal(got["t_two_pass"], got["t_folded"]) and torch.equal(got["g_two_pass"], got["g_folded"])
+    want_q, want_s = ops.quantize_e4m3(ops.rmsnorm(x, gain))
+    assert got["s_folded"].item() == pytest.approx(want_s.item(), rel=1e-2)
+    assert (got["q_folded"].view(torch.float8_e4m3fn).float() - want_q.float()).abs().max() <= 64   # same grid up to an ulp of y
+
+
 SKINNY_CASES = [
     (17, 1536, 1536, "bf16", "bias_gelu_res"), (17, 6144, 1536, "bf16", "bias_gelu"), (17, 1536, 6144, "bf16", "bias_res"),
     (4, 3072, 1536, "bf16", "bias"), (1, 1024, 64, "bf16", "bias"), (16, 1536, 32, "bf16", "bias"),
