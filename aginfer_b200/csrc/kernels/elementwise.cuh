@@ -70,6 +70,38 @@ extern "C" __global__ void agi_quantize_e4m3_bf16(const bf16* x, uint8_t* q, con
     q[i] = float_to_e4m3(__fdiv_rn(__bfloat162float(x[i]), scale));
 }
 
+// The same quantisation, written in the packed operand layout of the bulk-copy tensor-core GEMM
+// ("K-block-major, swizzled"): the 128-byte K block kb of row r goes to ((kb * rows_padded + r) * 128), its
+// 16-byte chunk c to position c ^ (r & 7).  One thread converts 16 consecutive values = one chunk.
+// cols % 16 == 0; rows past `rows` (up to rows_padded) are left as they are: the GEMM never stores them.
+extern "C" __global__ void agi_quantize_e4m3_packed_bf16(const bf16* x, uint8_t* q, const unsigned* amax_bits,
+                                                          float* scale_out, unsigned rows, unsigned cols,
+                                                          unsigned rows_padded) {
+  grid_dependency_wait();
+  const float amax = __uint_as_float(*amax_bits);
+  const float scale = amax > 0.f ? __fdiv_rn(amax, 448.f) : 1.f;
+  if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = scale;
+  const unsigned chunks_per_row = cols / 16;
+  const unsigned total = rows * chunks_per_row;
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const unsigned r = i / chunks_per_row, chunk = i % chunks_per_row;
+    const unsigned kb = chunk / 8, c = chunk % 8;
+    float f[16];
+    unpack8(*reinterpret_cast<const Bf16x8*>(x + size_t(r) * cols + chunk * 16), f);
+    unpack8(*reinterpret_cast<const Bf16x8*>(x + size_t(r) * cols + chunk * 16 + 8), f + 8);
+    unsigned words[4];
+#pragma unroll
+    for (int wd = 0; wd < 4; ++wd) {
+      unsigned word = 0;
+#pragma unroll
+      for (int b = 0; b < 4; ++b) word |= unsigned(float_to_e4m3(__fdiv_rn(f[wd * 4 + b], scale))) << (8 * b);
+      words[wd] = word;
+    }
+    uint8_t* dst = q + (size_t(kb) * rows_padded + r) * 128 + ((c ^ (r & 7)) << 4);
+    *reinterpret_cast<uint4*>(dst) = make_uint4(words[0], words[1], words[2], words[3]);
+  }
+}
+
 // out[r, c] = silu(gate[r, c]) * up[r, c]; gate/up may be column blocks of one wider buffer.  With kAmax the
 // maximum |out| (of the rounded values) is folded into *amax_bits for the dynamic quantisation that follows.
 template <bool kAmax>
@@ -151,6 +183,16 @@ extern "C" __global__ void agi_gather_rows_bf16(const bf16* table, const int* id
     if (id >= table_rows) id = table_rows - 1;  // ids are validated offline; clamp instead of faulting
     *reinterpret_cast<Bf16x8*>(out + size_t(r) * out_stride + c) =
         *reinterpret_cast<const Bf16x8*>(table + size_t(id) * cols + c);
+  }
+}
+
+// Strided row copy of 32-bit words: out[r, c] = in[r, c] for c < cols (e.g. the first 14 of 32 latent columns).
+extern "C" __global__ void agi_copy_rows_u32(const unsigned* in, unsigned* out, unsigned rows, unsigned cols,
+                                              unsigned in_stride, unsigned out_stride) {
+  grid_dependency_wait();
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < rows * cols; i += gridDim.x * blockDim.x) {
+    const unsigned r = i / cols, c = i % cols;
+    out[size_t(r) * out_stride + c] = in[size_t(r) * in_stride + c];
   }
 }
 

@@ -83,6 +83,16 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 // Make this thread's completed shared-memory writes visible to the tensor core's (async proxy) reads.
 __device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+// Bulk (TMA, no tensor map) copy of a contiguous run of global memory into shared memory; completion is
+// counted in bytes on an mbarrier armed with expect_bytes.
+__device__ __forceinline__ void bulk_copy(unsigned dst, const void* src, unsigned bytes, unsigned long long* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void expect_bytes(unsigned long long* bar, unsigned bytes) {
+  asm volatile("{ .reg .b64 t; mbarrier.arrive.expect_tx.shared::cta.b64 t, [%0], %1; }" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
 __device__ __forceinline__ void tmem_alloc(unsigned* slot, unsigned columns) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(columns) : "memory");
   asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -245,7 +255,12 @@ __device__ __forceinline__ void store_features4(const float t4[4], unsigned m, u
 
 // grid = (ceil(N / 128), ceil(M / TN), splits), block = 160 threads,
 // dynamic shared memory = stages * (16384 + TN * 128) + 1024.
-template <bool kFp8, int kCluster = 1>
+// kPacked: both operands are stored "K-block-major, swizzled" (see recipes/layout.py): the 128-byte K block kb
+// of row r lives at ((kb * rows_padded + r) * 128) with its 16-byte chunk c at position c ^ (r & 7), i.e. the
+// image of the shared-memory tile.  A ring slot is then filled by two bulk copies (16 KB of weights, TN * 128 B
+// of activations) issued by one thread, instead of 16-byte copies by 128 threads; `ldx` carries the padded
+// row count of the activation matrix.
+template <bool kFp8, int kCluster = 1, bool kPacked = false>
 __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, void* y, const bf16* bias,
                                           const bf16* residual, const float* scale_a, const float* scale_w,
                                           float* partial, unsigned* counters, unsigned* status, unsigned M,
@@ -281,7 +296,7 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
   if (warp == 0) TC_STAMP(32);
   if (tid == 0) {
     for (unsigned s = 0; s < stages; ++s) {
-      mbar_init(&full_bar[s], kProducers);
+      mbar_init(&full_bar[s], kPacked ? 1 : kProducers);
       mbar_init(&empty_bar[s], 1);
     }
     mbar_init(&accum_bar, 1);
@@ -320,13 +335,48 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
     for (unsigned j = 0; j < 8; ++j)
       if (j < a_rows) cp_async_16(dst + j * 2048, src + j * w_step);
   };
-  if (warp < 4)
+  // packed operands: tile (first row r0, K block kb) is one contiguous run
+  const unsigned w_rows_padded = ((N + 255u) / 256u) * 256u;   // packed weights are padded to whole 256-row tiles
+  const unsigned b_tile_bytes = TN * kRowBytes;
+  auto packed_weights = [&](unsigned i) {
+    bulk_copy(ring + (i % stages) * stage_bytes, w + (size_t(kb_begin + i) * w_rows_padded + n0) * kRowBytes, kATileBytes,
+              &full_bar[i % stages]);
+  };
+  auto packed_tokens = [&](unsigned i) {
+    bulk_copy(ring + (i % stages) * stage_bytes + kATileBytes, x + (size_t(kb_begin + i) * ldx + m0) * kRowBytes,
+              b_tile_bytes, &full_bar[i % stages]);
+  };
+  if (kPacked) {
+    if (tid == 0)
+      for (unsigned i = 0; i < early; ++i) {
+        expect_bytes(&full_bar[i], kATileBytes + b_tile_bytes);
+        packed_weights(i);
+      }
+  } else if (warp < 4) {
     for (unsigned i = 0; i < early; ++i) load_weights(i);
+  }
 
   grid_dependency_wait();
   if (warp == 0) TC_STAMP(35);
 
-  if (warp < 4) {
+  if (kPacked && warp < 4) {
+    // ---------------- warp 0 is the producer: two bulk copies per ring slot, issued by its lane 0 ----------------
+    // (the whole warp walks the loop so that it reaches the epilogue converged; warps 1-3 go straight there)
+    if (warp == 0) {
+      if (lane == 0)
+        for (unsigned i = 0; i < early; ++i) packed_tokens(i);
+      for (unsigned i = early; i < nkb; ++i) {
+        const unsigned s = i % stages;
+        mbar_wait(&empty_bar[s], (i / stages - 1) & 1, status, kTimeoutEmpty | s);
+        if (lane == 0) {
+          expect_bytes(&full_bar[s], kATileBytes + b_tile_bytes);
+          packed_weights(i);
+          packed_tokens(i);
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp < 4) {
     // ---------------- producers ----------------
     for (unsigned i = 0; i < nkb + kLag; ++i) {
       if (i < nkb) {
@@ -565,7 +615,7 @@ agi_gemm_tc_bf16_x16(const bf16* x, void* y, unsigned* status, unsigned M, unsig
 // Up to three GEMMs over the same activation matrix as ONE launch (Q | K | V, gate | up): part i multiplies
 // by w_i [N_i, K], scales by scale_a * sw_i, adds bias_i and writes y_i with row pitch ldy_i.  The parts'
 // 128-row tiles are laid end to end along grid.x = sum of ceil(N_i / 128); no split-K.
-#define AGI_TC_GROUP_KERNEL(NAME, TYPE, FP8)                                                                          \
+#define AGI_TC_GROUP_KERNEL(NAME, TYPE, FP8, PACKED)                                                                  \
   extern "C" __global__ void __launch_bounds__(tc::kThreads, 1)                                                      \
   NAME(const TYPE* x, const float* scale_a, unsigned* status, unsigned M, unsigned K, unsigned ldx, unsigned flags,   \
        unsigned TN, unsigned stages, const TYPE* w0, const bf16* bias0, const float* sw0, void* y0, unsigned N0,      \
@@ -582,12 +632,28 @@ agi_gemm_tc_bf16_x16(const bf16* x, void* y, unsigned* status, unsigned M, unsig
     } else if (tile >= t0) {                                                                                          \
       w = w1; bias = bias1; sw = sw1; y = y1; N = N1; ldy = ldy1; tile -= t0;                                         \
     }                                                                                                                 \
-    tc::gemm_body<FP8>(reinterpret_cast<const uint8_t*>(x), reinterpret_cast<const uint8_t*>(w), y, bias, bias,      \
-                       scale_a, sw, nullptr, nullptr, status, M, N, K, ldx, ldy, flags, TN, stages, tile);            \
+    tc::gemm_body<FP8, 1, PACKED>(reinterpret_cast<const uint8_t*>(x), reinterpret_cast<const uint8_t*>(w), y, bias,  \
+                                  bias, scale_a, sw, nullptr, nullptr, status, M, N, K, ldx, ldy, flags, TN, stages,  \
+                                  tile);                                                                              \
   }
-AGI_TC_GROUP_KERNEL(agi_gemm_tc_bf16_x3, bf16, false)
-AGI_TC_GROUP_KERNEL(agi_gemm_tc_e4m3_x3, uint8_t, true)
+AGI_TC_GROUP_KERNEL(agi_gemm_tc_bf16_x3, bf16, false, false)
+AGI_TC_GROUP_KERNEL(agi_gemm_tc_e4m3_x3, uint8_t, true, false)
+// the same over packed operands (bulk-copy producers; ldx = padded row count of the activation matrix)
+AGI_TC_GROUP_KERNEL(agi_gemm_tcp_e4m3_x3, uint8_t, true, true)
 #undef AGI_TC_GROUP_KERNEL
+
+// Single GEMM over packed operands, split-K slabs as in agi_gemm_tc_*.
+#define AGI_TC_PACKED_KERNEL(NAME, TYPE, FP8)                                                                         \
+  extern "C" __global__ void __launch_bounds__(tc::kThreads, 1)                                                      \
+  NAME(const TYPE* x, const TYPE* w, void* y, const bf16* bias, const bf16* residual, const float* scale_a,          \
+       const float* scale_w, float* partial, unsigned* counters, unsigned* status, unsigned M, unsigned N,           \
+       unsigned K, unsigned ldx, unsigned ldy, unsigned flags, unsigned TN, unsigned stages) {                       \
+    tc::gemm_body<FP8, 1, true>(reinterpret_cast<const uint8_t*>(x), reinterpret_cast<const uint8_t*>(w), y, bias,    \
+                                residual, scale_a, scale_w, partial, counters, status, M, N, K, ldx, ldy, flags, TN,  \
+                                stages);                                                                              \
+  }
+AGI_TC_PACKED_KERNEL(agi_gemm_tcp_e4m3, uint8_t, true)
+#undef AGI_TC_PACKED_KERNEL
 
 extern "C" __global__ void __launch_bounds__(tc::kThreads, 1)
 agi_gemm_tc_bf16(const bf16* x, const bf16* w, void* y, const bf16* bias, const bf16* residual, const float* scale_a,

@@ -33,7 +33,7 @@ constexpr unsigned kWideThreads = kWideProducers + 32;
 
 // grid = (ceil(N / 256), ceil(M / TN), splits), block = 288,
 // dynamic shared memory = stages * (32768 + TN * 128) + 1024; TN a multiple of 16, <= 256.
-template <bool kFp8>
+template <bool kFp8, bool kPacked = false>
 __device__ __forceinline__ void gemm_wide_body(const uint8_t* x, const uint8_t* w, void* y, const bf16* bias,
                                                const bf16* residual, const float* scale_a, const float* scale_w,
                                                float* partial, unsigned* counters, unsigned* status, unsigned M,
@@ -65,7 +65,7 @@ __device__ __forceinline__ void gemm_wide_body(const uint8_t* x, const uint8_t* 
 
   if (tid == 0) {
     for (unsigned s = 0; s < stages; ++s) {
-      mbar_init(&full_bar[s], kWideProducers);
+      mbar_init(&full_bar[s], kPacked ? 1 : kWideProducers);
       mbar_init(&empty_bar[s], 1);
     }
     mbar_init(&accum_bar, 1);
@@ -97,13 +97,48 @@ __device__ __forceinline__ void gemm_wide_body(const uint8_t* x, const uint8_t* 
     for (unsigned j = 0; j < 8; ++j)
       if (j < a_rows) cp_async_16(dst + j * 4096, src + j * w_step);
   };
+  // packed operands (see gemm_tc.cuh): a 256-row weight tile of one K block is one contiguous 32 KB run
+  const unsigned w_rows_padded = ((N + kRows - 1) / kRows) * kRows;
+  const unsigned b_tile_bytes = TN * kRowBytes;
+  auto packed_weights = [&](unsigned i) {
+    bulk_copy(ring + (i % stages) * stage_bytes, w + (size_t(kb_begin + i) * w_rows_padded + n0) * kRowBytes,
+              kWideATileBytes, &full_bar[i % stages]);
+  };
+  auto packed_tokens = [&](unsigned i) {
+    bulk_copy(ring + (i % stages) * stage_bytes + kWideATileBytes, x + (size_t(kb_begin + i) * ldx + m0) * kRowBytes,
+              b_tile_bytes, &full_bar[i % stages]);
+  };
   // Weights do not depend on the previous kernel: the first ring slots are requested before waiting for it.
-  if (warp < kMmaWarp)
+  if (kPacked) {
+    if (tid == 0)
+      for (unsigned i = 0; i < early; ++i) {
+        expect_bytes(&full_bar[i], kWideATileBytes + b_tile_bytes);
+        packed_weights(i);
+      }
+  } else if (warp < kMmaWarp) {
     for (unsigned i = 0; i < early; ++i) load_weights(i);
+  }
 
   grid_dependency_wait();
 
-  if (warp < kMmaWarp) {
+  if (kPacked && warp < kMmaWarp) {
+    // warp 0 is the producer: two bulk copies per ring slot, issued by its lane 0; the whole warp walks the
+    // loop so that it reaches the epilogue converged; the other warps go straight there
+    if (warp == 0) {
+      if (lane == 0)
+        for (unsigned i = 0; i < early; ++i) packed_tokens(i);
+      for (unsigned i = early; i < nkb; ++i) {
+        const unsigned s = i % stages;
+        mbar_wait(&empty_bar[s], (i / stages - 1) & 1, status, kTimeoutEmpty | s);
+        if (lane == 0) {
+          expect_bytes(&full_bar[s], kWideATileBytes + b_tile_bytes);
+          packed_weights(i);
+          packed_tokens(i);
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp < kMmaWarp) {
     // ---------------- producers ----------------
     for (unsigned i = 0; i < nkb + kLag; ++i) {
       if (i < nkb) {
@@ -252,4 +287,15 @@ agi_gemm_tc_wide_e4m3(const uint8_t* x, const uint8_t* w, void* y, const bf16* b
                       unsigned stages) {
   tcw::gemm_wide_body<true>(x, w, y, bias, residual, scale_a, scale_w, partial, counters, status, M, N, K, ldx, ldy,
                             flags, TN, stages);
+}
+
+// The same over packed operands (bulk-copy producers; ldx = padded row count of the activation matrix; the
+// weight matrix is padded to whole 256-row tiles).
+extern "C" __global__ void __launch_bounds__(tcw::kWideThreads, 1)
+agi_gemm_tcp_wide_e4m3(const uint8_t* x, const uint8_t* w, void* y, const bf16* bias, const bf16* residual,
+                       const float* scale_a, const float* scale_w, float* partial, unsigned* counters, unsigned* status,
+                       unsigned M, unsigned N, unsigned K, unsigned ldx, unsigned ldy, unsigned flags, unsigned TN,
+                       unsigned stages) {
+  tcw::gemm_wide_body<true, true>(x, w, y, bias, residual, scale_a, scale_w, partial, counters, status, M, N, K, ldx,
+                                  ldy, flags, TN, stages);
 }

@@ -32,6 +32,8 @@ FLAG_LAYERNORM, FLAG_LN_MODULATE, FLAG_SLAB = 1 << 10, 1 << 11, 1 << 12
 ACT = {None: 0, "gelu_tanh": 1 << 4, "silu": 2 << 4, "relu": 3 << 4}
 PLAN_DTYPE_BYTES = {"F32": 4, "F16": 2, "BF16": 2, "F8_E4M3": 1, "I32": 4}
 
+from .layout import padded_token_rows, padded_weight_rows
+
 
 @dataclass(frozen=True)
 class Tensor:
@@ -330,13 +332,23 @@ class RecipeBuilder:
         self.launch("vector_add_f32", (ceil_div(count, 256), 1, 1), (256, 1, 1), [left, right, out, U32(count)],
                     op="vector_add")
 
-    def quantize_e4m3(self, x: Pointer, q: Pointer, scale_out: Pointer, count: int, amax: Pointer | None = None) -> None:
+    def quantize_e4m3(self, x: Pointer, q: Pointer, scale_out: Pointer, count: int, amax: Pointer | None = None,
+                      packed: tuple[int, int] | None = None) -> None:
         """amax -> scale = amax / 448 -> q = e4m3(x / scale); two launches sharing one counter, or one launch
-        when the producer of ``x`` already folded max |x| into ``amax`` (a ``counter()`` slot)."""
+        when the producer of ``x`` already folded max |x| into ``amax`` (a ``counter()`` slot).
+        ``packed=(rows, cols)`` writes ``q`` in the packed operand layout of the bulk-copy GEMM
+        (``recipes/layout.py``; ``q`` needs ``padded_token_rows(rows) * cols`` bytes)."""
         blocks = grid_for(count // 8 + 1, 256, SM_COUNT * 4)
         if amax is None:
             amax = self.counter()
             self.launch("agi_absmax_bf16", (blocks, 1, 1), (256, 1, 1), [x, U32(count), amax], op="absmax")
+        if packed is not None:
+            rows, cols = packed
+            assert rows * cols == count and cols % 128 == 0
+            self.launch("agi_quantize_e4m3_packed_bf16", (grid_for(count // 16, 256, SM_COUNT * 4), 1, 1), (256, 1, 1),
+                        [x, q, amax, scale_out, U32(rows), U32(cols), U32(padded_token_rows(rows))],
+                        op="quantize_e4m3_packed")
+            return
         self.launch("agi_quantize_e4m3_bf16", (blocks, 1, 1), (256, 1, 1), [x, q, amax, scale_out, U32(count)],
                     op="quantize_e4m3")
 
@@ -429,8 +441,25 @@ class RecipeBuilder:
              bias: Pointer | None = None, residual: Pointer | None = None, act: str | None = None,
              scale_a: Pointer | None = None, scale_w: Pointer | None = None, ldx: int | None = None,
              ldy: int | None = None, out_f32: bool = False, tactic: str = "auto",
-             splits: int | None = None) -> None:
-        """Y[M, N] = epilogue(X[M, K] . W[N, K]^T); ``dtype`` names the operand type (bf16 or e4m3)."""
+             splits: int | None = None, packed: bool = False) -> None:
+        """Y[M, N] = epilogue(X[M, K] . W[N, K]^T); ``dtype`` names the operand type (bf16 or e4m3).
+        ``packed`` (E4M3 only): both operands are in the packed layout of ``recipes/layout.py`` (weights packed
+        at packaging time, activations by ``quantize_e4m3(..., packed=)``) and ring slots are filled by bulk copies."""
+        if packed:
+            assert dtype == "e4m3" and K % 128 == 0 and ldx is None
+            t = tc_prefill_plan(M, N, K, 1)
+            flags = ACT[act] | (FLAG_BIAS if bias else 0) | (FLAG_RESIDUAL if residual else 0) | \
+                (FLAG_OUT_F32 if out_f32 else 0) | (FLAG_SCALED if scale_a else 0)
+            dummy = Arena(0)
+            partial, counters = self._tc_scratch
+            wide = t["rows"] == 256
+            self.launch("agi_gemm_tcp_wide_e4m3" if wide else "agi_gemm_tcp_e4m3", (t["n_tiles"], t["m_tiles"], t["splits"]),
+                        (288 if wide else 160, 1, 1),
+                        [x, w, y, bias or dummy, residual or dummy, scale_a or dummy, scale_w or dummy, partial, counters,
+                         Arena(STATUS_WORD), U32(M), U32(N), U32(K), U32(padded_token_rows(M)), U32(ldy or N), U32(flags),
+                         U32(t["TN"]), U32(t["stages"])], shared_bytes=t["shared_bytes"], op="gemm_e4m3_packed",
+                        algorithm=f"tcgen05_bulk_{t['rows']}x{t['TN']}_s{t['stages']}_k{t['splits']}")
+            return
         flags = ACT[act] | (FLAG_BIAS if bias else 0) | (FLAG_RESIDUAL if residual else 0) | \
             (FLAG_OUT_F32 if out_f32 else 0) | (FLAG_SCALED if scale_a else 0)
         assert (scale_a is None) == (scale_w is None)
@@ -520,7 +549,7 @@ class RecipeBuilder:
 
     def gemm_group(self, x: Pointer, parts: Sequence[tuple[Pointer, Pointer | None, Pointer | None, Pointer, int, int]],
                    M: int, K: int, *, dtype: str = "bf16", scale_a: Pointer | None = None, ldx: int | None = None,
-                   act: str | None = None) -> None:
+                   act: str | None = None, packed: bool = False) -> None:
         """Up to three GEMMs over one activation matrix in one tensor-core launch (Q | K | V, gate | up).
         ``parts``: ``(weight, bias or None, weight scale or None, y, N, ldy)``; either every part has a bias
         or none has; with ``scale_a`` every part brings its weight scale."""
@@ -534,8 +563,9 @@ class RecipeBuilder:
         flags = ACT[act] | (FLAG_BIAS if has_bias else 0) | (FLAG_SCALED if scale_a else 0)
         t = tc_group_tiling(M, sum(ceil_div(p[4], 128) for p in parts), K, elem)
         dummy = Arena(0)
-        args: list[Any] = [x, scale_a or dummy, Arena(STATUS_WORD), U32(M), U32(K), U32(ldx or K), U32(flags),
-                           U32(t["TN"]), U32(t["stages"])]
+        assert not packed or (dtype == "e4m3" and ldx is None)
+        args: list[Any] = [x, scale_a or dummy, Arena(STATUS_WORD), U32(M), U32(K),
+                           U32(padded_token_rows(M) if packed else (ldx or K)), U32(flags), U32(t["TN"]), U32(t["stages"])]
         for i in range(3):
             if i < len(parts):
                 w, bias, sw, y, N, ldy = parts[i]
@@ -543,9 +573,9 @@ class RecipeBuilder:
             else:
                 args += [dummy, dummy, dummy, dummy, U32(0), U32(0)]
         grid_x = sum(ceil_div(p[4], 128) for p in parts)
-        self.launch(f"agi_gemm_tc_{dtype}_x3", (grid_x, t["m_tiles"], 1), (160, 1, 1), args,
-                    shared_bytes=t["shared_bytes"], op=f"gemm_{dtype}_group",
-                    algorithm=f"tcgen05_128x{t['TN']}_s{t['stages']}_x{len(parts)}")
+        self.launch(f"agi_gemm_tcp_{dtype}_x3" if packed else f"agi_gemm_tc_{dtype}_x3", (grid_x, t["m_tiles"], 1),
+                    (160, 1, 1), args, shared_bytes=t["shared_bytes"], op=f"gemm_{dtype}_group" + ("_packed" if packed else ""),
+                    algorithm=f"tcgen05_{'bulk_' if packed else ''}128x{t['TN']}_s{t['stages']}_x{len(parts)}")
 
     def gemm_batch(self, x: Pointer, parts: Sequence[tuple[Pointer, Pointer]], y: Pointer, M: int, N: int, K: int,
                    seg_stride: int, ldx: int | None = None) -> None:

@@ -23,7 +23,7 @@ GEMM_SHAPES = {"gemm_q": (D, D), "gemm_fc1": (MLP, D), "gemm_fc2": (D, MLP),
 CASES = ("empty", "layernorm", "attn_self", "attn_cross", *GEMM_SHAPES)
 
 
-def build(case: str, tactic: str, reps: int, tokens: int, stages: int = 4, dtype: str = "bf16"):
+def build(case: str, tactic: str, reps: int, tokens: int, stages: int = 4, dtype: str = "bf16", packed: bool = False):
     import torch
 
     from . import Arena, RecipeBuilder, Tensor, U32, Weight, io
@@ -37,10 +37,13 @@ def build(case: str, tactic: str, reps: int, tokens: int, stages: int = 4, dtype
             w = torch.randn(n, k, generator=g) * 0.02
             weights[f"l{l}.w"] = w.to(torch.bfloat16) if dtype == "bf16" else w.clamp(-0.08, 0.08).mul(448 / 0.08).to(
                 torch.float8_e4m3fn)
+            if packed:
+                from .layout import pack_kblock_swizzled
+                weights[f"l{l}.w"] = pack_kblock_swizzled(weights[f"l{l}.w"])
         weights["w_scale"] = torch.tensor(0.08 / 448, dtype=torch.float32)
     r = RecipeBuilder(describe(weights))
     r.begin_profile("default", [io("token", "I32", [1])], [io("status", "I32", [1])])
-    big = max(tokens, 64) * 11008 * 2
+    big = (max(tokens, 64) + 512) * 11008 * 2     # room for the padded rows of packed activations
     x, y, scale_a = r.alloc(big), r.alloc(big), r.alloc(4)
     kbuf, vbuf, q = r.alloc(300 * D * 2), r.alloc(300 * D * 2), r.alloc(64 * D * 2)
     for i in range(reps):
@@ -58,7 +61,7 @@ def build(case: str, tactic: str, reps: int, tokens: int, stages: int = 4, dtype
                 r.gemm(x, Weight(f"l{i % LAYERS}.w"), y, tokens, n, k, tactic=tactic)
             else:   # activations taken as already quantised bytes; scales are whatever the arena holds
                 r.gemm(x, Weight(f"l{i % LAYERS}.w"), y, tokens, n, k, dtype="e4m3", scale_a=scale_a,
-                       scale_w=Weight("w_scale"), tactic=tactic)
+                       scale_w=Weight("w_scale"), tactic=tactic, packed=packed)
     r.export_status(Tensor("status"))
     return weights, r
 
@@ -78,10 +81,11 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=T)
     ap.add_argument("--pdl", action="store_true")
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "e4m3"])
+    ap.add_argument("--packed", action="store_true", help="e4m3 only: packed operands, bulk-copy producers")
     ap.add_argument("--stages", type=int, default=4, help="K partitions of the bulk-stream GEMM (1-4)")
     args = ap.parse_args()
 
-    weights, recipe = build(args.case, args.tactic, args.reps, args.tokens, args.stages, args.dtype)
+    weights, recipe = build(args.case, args.tactic, args.reps, args.tokens, args.stages, args.dtype, args.packed)
     with tempfile.TemporaryDirectory() as tmp:
         aim = build_aim(Path(tmp), weights, recipe)
         runner = Runner(aim, flags=rt.PROGRAMMATIC_LAUNCH if args.pdl else 0)
@@ -99,7 +103,7 @@ def main() -> None:
             end.record(stream)
             torch.cuda.synchronize()
         us = start.elapsed_time(end) * 1000.0 / args.iters / (args.reps + 2)
-        line = f"{args.case} tactic={args.tactic} tokens={args.tokens} pdl={args.pdl}: {us:.2f} us/launch"
+        line = f"{args.case} tactic={args.tactic} tokens={args.tokens} pdl={args.pdl} packed={args.packed}: {us:.2f} us/launch"
         if args.case in GEMM_SHAPES:
             n, k = GEMM_SHAPES[args.case]
             elem = 2 if args.dtype == "bf16" else 1

@@ -33,13 +33,16 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--vocab", type=int, default=151936)
     ap.add_argument("--tactic", default="auto")
+    ap.add_argument("--packed", action="store_true", help="packed weights / activations, bulk-copy GEMM producers")
     ap.add_argument("--save-outputs", default=None, help="write hidden_out / kv_cache / status as a .pt file")
     args = ap.parse_args()
     full = tuple(i for i in (7, 15, 23, 31) if i < args.v_layers) or (args.v_layers - 1,)
     cfg = qwen_vl.VlConfig(v_layers=args.v_layers, v_full_layers=full, layers=args.layers, vocab=args.vocab)
     t0 = time.time()
     weights, inputs = qwen_vl.synthetic_weights(cfg), qwen_vl.synthetic_inputs(cfg)
-    recipe = qwen_vl.build_recipe(cfg, describe(weights), gemm_tactic=args.tactic)
+    if args.packed:
+        weights = qwen_vl.pack_checkpoint(weights)
+    recipe = qwen_vl.build_recipe(cfg, describe(weights), gemm_tactic=args.tactic, packed=args.packed)
     scratch = Path("/dev/shm") if Path("/dev/shm").is_dir() else None      # 2 x 4 GB of files: prefer memory
     tmp = Path(tempfile.mkdtemp(prefix="agi_prefill_", dir=scratch))
     try:
@@ -65,7 +68,7 @@ def main() -> None:
         print(json.dumps({
             "workload": f"qwen2.5-vl-shaped fp8 prefill, {cfg.v_layers} vision blocks + {cfg.layers} decoder layers, "
                         f"{cfg.patches} patches, {cfg.tokens} tokens",
-            "ms_per_prefill": ms, "launches": int(stats["launches_per_enqueue"]), "pdl": args.pdl,
+            "ms_per_prefill": ms, "launches": int(stats["launches_per_enqueue"]), "pdl": args.pdl, "packed": args.packed,
             "fp8_weight_gb": alg["fp8_weight_bytes"] / 1e9, "weight_stream_gbs": alg["fp8_weight_bytes"] / ms / 1e6,
             "tflops": alg["flops"] / ms / 1e9, "status": int(out["status"].item()),
             "setup_s": {"weights_and_package": t1 - t0, "load_and_first_runs": time.time() - t1 - ms * args.iters / 1e3},

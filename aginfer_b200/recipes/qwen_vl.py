@@ -27,6 +27,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 
 from .builder import RecipeBuilder, Tensor, U32, Weight, ceil_div, grid_for, io
+from .layout import pack_kblock_swizzled, padded_token_rows
 
 
 @dataclass(frozen=True)
@@ -166,6 +167,15 @@ def synthetic_weights(cfg: VlConfig, seed: int = 3, std: float = 0.02) -> dict:
     return out
 
 
+def pack_checkpoint(weights: dict) -> dict:
+    """Packaging-time layout pass: every E4M3 linear weight [N, K] is replaced (same name) by its packed form
+    [K / 128, N padded to 256, 128] for the bulk-copy tensor-core GEMM (see ``layout.py``).  The values are
+    untouched, so the oracle keeps using the row-major checkpoint."""
+    import torch
+    return {k: pack_kblock_swizzled(v) if v.dtype == torch.float8_e4m3fn and v.dim() == 2 else v
+            for k, v in weights.items()}
+
+
 def rope_positions(cfg: VlConfig):
     """M-RoPE position streams [3, tokens] int32 for [image 0 | image 1 | ... | text]."""
     import torch
@@ -192,25 +202,32 @@ def synthetic_inputs(cfg: VlConfig, seed: int = 3) -> dict:
 
 
 def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto", trace: bool = False,
-                 group: bool = True) -> RecipeBuilder:
+                 group: bool = True, packed: bool = False, extra_inputs=(), extra_outputs=(), tail=None,
+                 extra_counters: int = 0) -> RecipeBuilder:
     """``weights``: name -> (dtype, shape) as from ``package.describe``.  ``trace`` adds three outputs for
     block-by-block checks: ``vision_trace`` [v_layers + 1, patches, 1280] (the patch embedding, then every
     block's output), ``merged_out`` [merged, hidden] (window order) and ``hidden_trace``
     [layers + 1, tokens, hidden] (the assembled prefix, then every decoder layer's output).  ``group`` runs the
-    projections that share an input (Q | K | V, gate | up) as one launch each."""
+    projections that share an input (Q | K | V, gate | up) as one launch each.  ``packed``: ``weights`` describes
+    a checkpoint that went through ``pack_checkpoint``; activations are quantised into the same layout and every
+    FP8 GEMM fills its ring with bulk copies.  ``tail(recipe, cache, hidden)`` appends launches that consume the
+    prefill inside the same profile (an action expert reading the K/V cache), with ``extra_inputs`` /
+    ``extra_outputs`` added to the profile's interface."""
     BF = 2
     P, VH, VD, VI = cfg.patches, cfg.v_hidden, cfg.v_head_dim, cfg.v_mlp_padded
     S, H, I, D = cfg.tokens, cfg.hidden, cfg.intermediate, cfg.head_dim
     G = cfg.grid // cfg.merge
-    r = RecipeBuilder(weights, counter_slots=4 * (cfg.v_layers + cfg.layers) + 8)   # one per quantisation
+    r = RecipeBuilder(weights, counter_slots=4 * (cfg.v_layers + cfg.layers) + 8 + extra_counters)   # one per quantisation
     r.begin_profile("default",
                     [io("pixels", "F32", [cfg.images, cfg.channels, cfg.image_size, cfg.image_size]),
-                     io("input_ids", "I32", [cfg.text_tokens]), io("positions", "I32", [3, S])],
+                     io("input_ids", "I32", [cfg.text_tokens]), io("positions", "I32", [3, S]), *extra_inputs],
                     [io("hidden_out", "BF16", [S, H]), io("kv_cache", "BF16", [cfg.layers, 2, S, cfg.kv_dim]),
-                     io("status", "I32", [1])] + ([io("vision_trace", "BF16", [cfg.v_layers + 1, P, VH]),
+                     io("status", "I32", [1]), *extra_outputs] + ([io("vision_trace", "BF16", [cfg.v_layers + 1, P, VH]),
                                                    io("merged_out", "BF16", [cfg.merged, H]),
                                                    io("hidden_trace", "BF16", [cfg.layers + 1, S, H])] if trace else []))
-    quant, scale = r.alloc(max(P * max(VH, VI), cfg.merged * cfg.merged_dim, S * max(H, I, cfg.q_dim))), r.alloc(4)
+    rows_of = padded_token_rows if packed else (lambda m: m)
+    quant = r.alloc(max(rows_of(P) * max(VH, VI), rows_of(cfg.merged) * cfg.merged_dim, rows_of(S) * max(H, I, cfg.q_dim)))
+    scale = r.alloc(4)
 
     traces: list[tuple[object, str, int]] = []       # (arena buffer, output tensor, bytes): copied out at the end
 
@@ -222,7 +239,7 @@ def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto", trace: bool 
             traces.append((keep, name, index, nbytes))
 
     def quantize(x, rows: int, K: int, amax=None):
-        r.quantize_e4m3(x, quant, scale, rows * K, amax=amax)
+        r.quantize_e4m3(x, quant, scale, rows * K, amax=amax, packed=(rows, K) if packed else None)
 
     def norm_quantize(x, gain: str, y, rows: int, cols: int, q_rows: int | None = None, q_cols: int | None = None):
         """RMSNorm that also leaves max |y| behind, then the E4M3 quantisation of y (viewed [q_rows, q_cols])."""
@@ -240,7 +257,7 @@ def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto", trace: bool 
         if group and gemm_tactic == "auto":
             r.gemm_group(quant, [(Weight(f"{n}.weight"), Weight(f"{n}.bias") if f"{n}.bias" in weights else None,
                                   Weight(f"{n}.weight_scale"), y, N, ldy) for n, y, N, ldy in parts], M, K,
-                         dtype="e4m3", scale_a=scale)
+                         dtype="e4m3", scale_a=scale, packed=packed)
         else:
             for n, y, N, ldy in parts:
                 linear_q(n, y, M, N, K, ldy=ldy)
@@ -249,7 +266,7 @@ def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto", trace: bool 
         """FP8 GEMM over the activations last quantised into ``quant``."""
         bias = Weight(f"{name}.bias") if f"{name}.bias" in weights else None
         r.gemm(quant, Weight(f"{name}.weight"), y, M, N, K, dtype="e4m3", scale_a=scale,
-               scale_w=Weight(f"{name}.weight_scale"), bias=bias, tactic=gemm_tactic, **kw)
+               scale_w=Weight(f"{name}.weight_scale"), bias=bias, tactic=gemm_tactic, packed=packed, **kw)
 
     # ---------------- vision tower ----------------
     patches, vpos = r.alloc(P * cfg.patch_k * BF), r.alloc(3 * P * 4)
@@ -322,6 +339,8 @@ def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto", trace: bool 
     words = cfg.layers * 2 * S * cfg.kv_dim * BF // 4
     r.launch("agi_copy_u32", (grid_for(words), 1, 1), (256, 1, 1), [cache, Tensor("kv_cache"), U32(words)],
              op="export_kv_cache")
+    if tail is not None:
+        tail(r, cache, h)
     r.export_status(Tensor("status"))
     # trace outputs are whole tensors: gather the kept copies of one output into a contiguous run, copy once
     for name in ("vision_trace", "merged_out", "hidden_trace"):

@@ -380,6 +380,69 @@ def test_producers_that_fold_the_amax_match_the_separate_pass(tmp_path):
     assert (got["q_folded"].view(torch.float8_e4m3fn).float() - want_q.float()).abs().max() <= 64   # same grid up to an ulp of y
 
 
+PACKED_CASES = [(288, 2048, 2048, "bias"), (1024, 11008, 2048, "plain"), (288, 2048, 11008, "res"),
+                (130, 300, 256, "bias_gelu"), (512, 1280, 3456, "bias_res"), (17, 128, 128, "plain")]
+
+
+@pytest.mark.parametrize("case", PACKED_CASES, ids=lambda c: "-".join(map(str, c)))
+def test_gemm_packed_operands(tmp_path, case):
+    """Bulk-copy tcgen05 GEMM: weights packed on the CPU (K-block-major, swizzled), activations quantised into
+    the same layout on the device; same arithmetic as the row-major kernels."""
+    from aginfer_b200.recipes.layout import pack_kblock_swizzled, padded_token_rows
+    M, N, K, epi = case
+    x, wf = randn(M, K, seed=91), randn(N, K, seed=92, std=0.02)
+    bias = randn(N, seed=93, std=0.1) if "bias" in epi else None
+    res = randn(M, N, seed=94) if "res" in epi else None
+    act = "gelu_tanh" if "gelu" in epi else None
+    wq, ws = ops.quantize_e4m3(wf)
+    xq, xs = ops.quantize_e4m3(x)
+    want = ops.gemm(xq, wq, bias=bias, residual=res, act=act, scale_a=xs, scale_w=ws)
+    weights = {"w": pack_kblock_swizzled(wq), "w_scale": ws.reshape(())}
+    inputs = {"x": x}
+    if bias is not None:
+        weights["b"] = bias
+    if res is not None:
+        inputs["res"] = res
+
+    def body(r):
+        q, s = r.alloc(padded_token_rows(M) * K), r.alloc(4)
+        r.quantize_e4m3(Tensor("x"), q, s, M * K, packed=(M, K))
+        r.gemm(q, Weight("w"), Tensor("y"), M, N, K, dtype="e4m3", scale_a=s, scale_w=Weight("w_scale"),
+               bias=Weight("b") if bias is not None else None, residual=Tensor("res") if res is not None else None,
+               act=act, packed=True)
+        r.export_status(Tensor("status"))
+
+    got, _ = run_recipe(tmp_path, weights, inputs, {"y": (BF, (M, N)), "status": (torch.int32, (1,))}, body, repeats=3)
+    assert got["status"].item() == 0, hex(got["status"].item())
+    assert ops.max_rel_err(got["y"], want) < 1e-2
+
+
+def test_gemm_group_packed_operands(tmp_path):
+    from aginfer_b200.recipes.layout import pack_kblock_swizzled, padded_token_rows
+    M, K, widths = 288, 2048, (2048, 256, 256)
+    x = randn(M, K, seed=95)
+    xq, xs = ops.quantize_e4m3(x)
+    weights, wants = {}, []
+    for i, n in enumerate(widths):
+        wq, ws = ops.quantize_e4m3(randn(n, K, seed=96 + i, std=0.02))
+        bias = randn(n, seed=99 + i, std=0.1)
+        weights.update({f"w{i}": pack_kblock_swizzled(wq), f"s{i}": ws.reshape(()), f"b{i}": bias})
+        wants.append(ops.gemm(xq, wq, bias=bias, scale_a=xs, scale_w=ws))
+
+    def body(r):
+        q, s = r.alloc(padded_token_rows(M) * K), r.alloc(4)
+        r.quantize_e4m3(Tensor("x"), q, s, M * K, packed=(M, K))
+        r.gemm_group(q, [(Weight(f"w{i}"), Weight(f"b{i}"), Weight(f"s{i}"), Tensor(f"y{i}"), n, n)
+                         for i, n in enumerate(widths)], M, K, dtype="e4m3", scale_a=s, packed=True)
+        r.export_status(Tensor("status"))
+
+    outs = {f"y{i}": (BF, (M, n)) for i, n in enumerate(widths)}
+    got, _ = run_recipe(tmp_path, weights, {"x": x}, {**outs, "status": (torch.int32, (1,))}, body, repeats=2)
+    assert got["status"].item() == 0
+    for i, want in enumerate(wants):
+        assert ops.max_rel_err(got[f"y{i}"], want) < 1e-2, i
+
+
 SKINNY_CASES = [
     (17, 1536, 1536, "bf16", "bias_gelu_res"), (17, 6144, 1536, "bf16", "bias_gelu"), (17, 1536, 6144, "bf16", "bias_res"),
     (4, 3072, 1536, "bf16", "bias"), (1, 1024, 64, "bf16", "bias"), (16, 1536, 32, "bf16", "bias"),

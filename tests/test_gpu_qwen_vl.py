@@ -37,8 +37,10 @@ def test_patchify_and_unwindow_are_bit_exact(tmp_path):
     assert torch.equal(got["raster"], oracle_vl.unwindow(cfg, merged))
 
 
-def run_prefill(tmp_path, cfg, w, x, trace=False):
-    aim = build_aim(tmp_path, w, qwen_vl.build_recipe(cfg, describe(w), trace=trace))
+def run_prefill(tmp_path, cfg, w, x, trace=False, packed=False):
+    if packed:
+        w = qwen_vl.pack_checkpoint(w)
+    aim = build_aim(tmp_path, w, qwen_vl.build_recipe(cfg, describe(w), trace=trace, packed=packed))
     runner = Runner(aim)
     dev = {k: v.cuda() for k, v in x.items()}
     out = runner.empty_outputs()
@@ -48,7 +50,8 @@ def run_prefill(tmp_path, cfg, w, x, trace=False):
     return {k: v.cpu() for k, v in out.items()}, runner.stats()
 
 
-def test_reduced_depth_prefill_matches_oracle_block_by_block(tmp_path):
+@pytest.mark.parametrize("packed", [False, True], ids=["row_major", "packed"])
+def test_reduced_depth_prefill_matches_oracle_block_by_block(tmp_path, packed):
     """Real widths and token counts; 4 vision blocks (the last with full attention) and 4 decoder layers.
 
     Every GEMM input is quantised per tensor with a scale taken from the tensor's largest element, so a
@@ -59,7 +62,7 @@ def test_reduced_depth_prefill_matches_oracle_block_by_block(tmp_path):
     merger and final norm, which have at most one quantisation upstream, at 2e-2; indexing bit-exact."""
     cfg = qwen_vl.VlConfig(v_layers=4, v_full_layers=(3,), layers=4, vocab=4096)
     w, x = qwen_vl.synthetic_weights(cfg), qwen_vl.synthetic_inputs(cfg)
-    got, stats = run_prefill(tmp_path, cfg, w, x, trace=True)
+    got, stats = run_prefill(tmp_path, cfg, w, x, trace=True, packed=packed)
     assert got["status"].item() == 0
     patches, pos = oracle_vl.patchify(cfg, x["pixels"])
     vt, ht = got["vision_trace"], got["hidden_trace"]

@@ -128,3 +128,23 @@ def test_fp8_block_tolerance_is_the_oracles_own_resolution():
         worst = max(worst, ops.max_rel_err(out, ref))
         assert ops.cosine(out, ref) > 0.999
     assert 1e-2 < worst < ops.FP8_BLOCK_TOL, worst
+
+
+def test_packed_layout_round_trip_and_addressing():
+    from aginfer_b200.recipes.layout import (pack_kblock_swizzled, padded_token_rows, padded_weight_rows,
+                                             unpack_kblock_swizzled)
+    w = (torch.randn(300, 384, generator=torch.Generator().manual_seed(2)) * 50).to(torch.float8_e4m3fn)
+    p = pack_kblock_swizzled(w)
+    assert p.shape == (3, 512, 128) and p.dtype == torch.float8_e4m3fn and padded_weight_rows(300) == 512
+    assert torch.equal(unpack_kblock_swizzled(p, 300).view(torch.uint8), w.view(torch.uint8))
+    raw, src = p.view(torch.uint8).reshape(-1), w.view(torch.uint8)
+    for r, kbyte in ((0, 0), (77, 200), (299, 383), (130, 129)):
+        kb, c, b = kbyte // 128, (kbyte % 128) // 16, kbyte % 16
+        assert raw[(kb * 512 + r) * 128 + ((c ^ (r & 7)) << 4) + b] == src[r, kbyte]
+    assert raw.reshape(3, 512, 128)[:, 300:].max() == 0                       # padding rows are zero
+    h = torch.randn(16, 64).to(torch.bfloat16)                                 # two-byte elements: 64 per block
+    assert torch.equal(unpack_kblock_swizzled(pack_kblock_swizzled(h), 16), h)
+    assert padded_token_rows(288) == 768 and padded_token_rows(256) == 512
+    packed = qwen_vl.pack_checkpoint(qwen_vl.synthetic_weights(SMALL))
+    assert packed["model.layers.0.mlp.down_proj.weight"].shape == (86, 2048, 128)
+    assert packed["model.embed_tokens.weight"].shape == (512, 2048)           # bf16 tensors are left alone
