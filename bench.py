@@ -207,7 +207,17 @@ def run_ours(args) -> None:
     ms_e2e = timed(chunk_e2e, e2e_steps)
     clocks = sampler.stop(t0, t1) if sampler is not None else None
 
-    ms, ms_e2e = group.max_over_ranks([ms, ms_e2e])
+    # ---- the same chunk as plain launches (no graph replay): what a loader without graph templates would do ----
+    plain = Runner(aim, profile="default", flags=session_flags | rt.NO_GRAPH_REPLAY)
+    plain_chunk = lambda: plain.run(dev_in, out, stream=stream)
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            plain_chunk()
+    plain_steps = max(3, min(args.steps, 50))
+    ms_plain = timed(plain_chunk, plain_steps) / plain_steps
+    del plain
+
+    ms, ms_e2e, ms_plain = group.max_over_ranks([ms, ms_e2e, ms_plain])
     stats = runner.stats()
 
     result = None
@@ -224,6 +234,7 @@ def run_ours(args) -> None:
                        "launch_mode": "one CUDA graph per chunk, built by the loader on the first Enqueue; "
                                       + ("plain edges" if args.no_pdl else "programmatic dependent launch edges")},
             "latency_ms_per_action_chunk": ms / args.steps,
+            "latency_ms_per_action_chunk_plain_launches": ms_plain,
             "chunk_weight_bytes": acc["per_chunk"],
             "chunk_hbm_frac_of_%s" % peak_kind: acc["per_chunk"] / (ms / args.steps / 1000.0) / 1e9 / peak,
             "e2e": {"value": group.whole_job_rate(e2e_steps, ms_e2e), "unit": UNIT, "h2d_bytes_per_step": h2d,
