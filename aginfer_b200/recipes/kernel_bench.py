@@ -20,7 +20,7 @@ GEMM_SHAPES = {"gemm_q": (D, D), "gemm_fc1": (MLP, D), "gemm_fc2": (D, MLP),
                # the (N, K) grid of the FP8 GEMM sweep
                "gemm_2048x2048": (2048, 2048), "gemm_11008x2048": (11008, 2048), "gemm_2048x11008": (2048, 11008),
                "gemm_2560x2048": (2560, 2048), "gemm_1536x1536": (1536, 1536), "gemm_6144x1536": (6144, 1536)}
-CASES = ("empty", "layernorm", "attn_self", "attn_cross", *GEMM_SHAPES)
+CASES = ("empty", "layernorm", "attn_self", "attn_cross", "attn_prefill", "attn_vision", *GEMM_SHAPES)
 
 
 def build(case: str, tactic: str, reps: int, tokens: int, stages: int = 4, dtype: str = "bf16", packed: bool = False):
@@ -45,7 +45,8 @@ def build(case: str, tactic: str, reps: int, tokens: int, stages: int = 4, dtype
     r.begin_profile("default", [io("token", "I32", [1])], [io("status", "I32", [1])])
     big = (max(tokens, 64) + 512) * 11008 * 2     # room for the padded rows of packed activations
     x, y, scale_a = r.alloc(big), r.alloc(big), r.alloc(4)
-    kbuf, vbuf, q = r.alloc(300 * D * 2), r.alloc(300 * D * 2), r.alloc(64 * D * 2)
+    attn_bytes = max(tokens, 300) * 2048 * 2       # the widest attention operand of any case
+    kbuf, vbuf, q = r.alloc(attn_bytes), r.alloc(attn_bytes), r.alloc(attn_bytes)
     for i in range(reps):
         if case == "empty":
             r.launch("agi_fill_u32", (1, 1, 1), (256, 1, 1), [Arena(64), U32(0), U32(16)])
@@ -55,6 +56,12 @@ def build(case: str, tactic: str, reps: int, tokens: int, stages: int = 4, dtype
             kv_rows = tokens if case == "attn_self" else 300
             r.attention(q, kbuf, vbuf, y, q_rows=tokens, kv_rows=kv_rows, q_heads=32, kv_heads=32, head_dim=48,
                         q_stride=D, k_stride=D, v_stride=D, o_stride=D)
+        elif case == "attn_prefill":      # decoder prefill: `tokens` causal rows, 16 query / 2 KV heads of 128
+            r.attention(q, kbuf, vbuf, y, q_rows=tokens, kv_rows=tokens, q_heads=16, kv_heads=2, head_dim=128,
+                        q_stride=2048, k_stride=256, v_stride=256, o_stride=2048, mask="causal")
+        elif case == "attn_vision":       # vision tower: `tokens` patch rows, 16 heads of 80, 64-token windows
+            r.attention(q, kbuf, vbuf, y, q_rows=tokens, kv_rows=tokens, q_heads=16, kv_heads=16, head_dim=80,
+                        q_stride=1280, k_stride=1280, v_stride=1280, o_stride=1280, mask="block", mask_arg=64)
         else:
             n, k = GEMM_SHAPES[case]
             if dtype == "bf16":
