@@ -26,7 +26,7 @@ template <int HD16>
 __device__ __forceinline__ void attention_body(const bf16* q, const bf16* k, const bf16* v, bf16* o, unsigned q_rows,
                                                unsigned kv_rows, unsigned q_heads, unsigned kv_heads, unsigned q_stride,
                                                unsigned k_stride, unsigned v_stride, unsigned o_stride, float scale,
-                                               unsigned mask_mode, unsigned mask_arg) {
+                                               unsigned mask_mode, unsigned mask_arg, unsigned* amax_bits = nullptr) {
   constexpr unsigned head_dim = HD16 * 16, pitch = head_dim + 8, vec_per_row = head_dim / 8;
   extern __shared__ __align__(16) unsigned char attn_smem[];
   bf16* tiles = reinterpret_cast<bf16*>(attn_smem);   // [2 buffers][K | V][64][pitch]
@@ -170,6 +170,7 @@ __device__ __forceinline__ void attention_body(const bf16* q, const bf16* k, con
     __syncthreads();   // everyone is done with this buffer before it is refilled
   }
 
+  float best = 0.f;   // max |o| over this thread's outputs, for a following dynamic quantisation
 #pragma unroll
   for (int hr = 0; hr < 2; ++hr) {
     const unsigned row = warp_row + g + hr * 8;
@@ -177,8 +178,16 @@ __device__ __forceinline__ void attention_body(const bf16* q, const bf16* k, con
     const float inv = row_sum[hr] > 0.f ? 1.f / row_sum[hr] : 0.f;
     bf16* dst = o + size_t(row) * o_stride + head * head_dim + 2 * t;
 #pragma unroll
-    for (int nt = 0; nt < 2 * HD16; ++nt)
-      *reinterpret_cast<bf162*>(dst + nt * 8) = __floats2bfloat162_rn(out[nt][2 * hr] * inv, out[nt][2 * hr + 1] * inv);
+    for (int nt = 0; nt < 2 * HD16; ++nt) {
+      const float a = out[nt][2 * hr] * inv, b = out[nt][2 * hr + 1] * inv;
+      best = fmaxf(best, fmaxf(fabsf(a), fabsf(b)));
+      *reinterpret_cast<bf162*>(dst + nt * 8) = __floats2bfloat162_rn(a, b);
+    }
+  }
+  if (amax_bits != nullptr) {   // rounding is monotonic: the rounded maximum is the maximum of the rounded outputs
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, offset));
+    if (lane == 0) atomicMax(amax_bits, __float_as_uint(__bfloat162float(__float2bfloat16_rn(best))));
   }
 }
 
@@ -192,6 +201,18 @@ __device__ __forceinline__ void attention_body(const bf16* q, const bf16* k, con
     fa::attention_body<HD16>(q, k, v, o, q_rows, kv_rows, q_heads, kv_heads, q_stride, k_stride, v_stride, o_stride, \
                              scale, mask_mode, mask_arg);                                                            \
   }
+// the same, also folding max |o| into *amax_bits (a zero-initialised word)
+#define AGI_ATTENTION_FA_AMAX(NAME, HD16)                                                                            \
+  extern "C" __global__ void __launch_bounds__(128)                                                                  \
+  NAME(const bf16* q, const bf16* k, const bf16* v, bf16* o, unsigned q_rows, unsigned kv_rows, unsigned q_heads,    \
+       unsigned kv_heads, unsigned head_dim, unsigned q_stride, unsigned k_stride, unsigned v_stride,               \
+       unsigned o_stride, float scale, unsigned mask_mode, unsigned mask_arg, unsigned* amax_bits) {                 \
+    fa::attention_body<HD16>(q, k, v, o, q_rows, kv_rows, q_heads, kv_heads, q_stride, k_stride, v_stride, o_stride, \
+                             scale, mask_mode, mask_arg, amax_bits);                                                 \
+  }
+AGI_ATTENTION_FA_AMAX(agi_attention_fa_amax_bf16_d80, 5)
+AGI_ATTENTION_FA_AMAX(agi_attention_fa_amax_bf16_d128, 8)
+#undef AGI_ATTENTION_FA_AMAX
 AGI_ATTENTION_FA(agi_attention_fa_bf16_d48, 3)
 AGI_ATTENTION_FA(agi_attention_fa_bf16_d64, 4)
 AGI_ATTENTION_FA(agi_attention_fa_bf16_d80, 5)

@@ -9,5 +9,6 @@
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
 #include "gemm_tc_wide.cuh"
+#include "gemm_tc_persist.cuh"
 #include "gemm_skinny.cuh"
 #include "gemm_stream.cuh"

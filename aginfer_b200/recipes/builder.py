@@ -389,7 +389,9 @@ class RecipeBuilder:
     def attention(self, q: Pointer, k: Pointer, v: Pointer, o: Pointer, *, q_rows: int, kv_rows: int, q_heads: int,
                   kv_heads: int, head_dim: int, q_stride: int, k_stride: int, v_stride: int, o_stride: int,
                   mask: str = "none", mask_arg: int = 0, scale: float | None = None,
-                  algorithm: str = "auto") -> None:
+                  algorithm: str = "auto", amax: Pointer | None = None) -> None:
+        """``amax`` (a ``counter()`` slot; head widths 80 and 128, streaming tensor-core kernel only): the kernel
+        also leaves max |o| there for a following ``quantize_e4m3(..., amax=)``."""
         assert head_dim <= 128 and head_dim % 2 == 0 and q_heads % kv_heads == 0
         mode = {"none": 0, "causal": 1, "block": 2}[mask]
         args = [q, k, v, o, U32(q_rows), U32(kv_rows), U32(q_heads), U32(kv_heads), U32(head_dim), U32(q_stride),
@@ -409,6 +411,12 @@ class RecipeBuilder:
             # few query rows: one block per head, tensor-core scores and P.V
             self.launch("agi_attention_mma_bf16", (q_heads, ceil_div(q_rows, 16), 1), (256, 1, 1), args, shared_bytes=mma_smem,
                         op=f"attention_{mask}", algorithm="mma_key_split")
+            return
+        if amax is not None:
+            assert aligned and head_dim in (80, 128) and q_stride % 2 == 0 and o_stride % 2 == 0 and (q_rows > 64 or head_dim > 64)
+            self.launch(f"agi_attention_fa_amax_bf16_d{head_dim}", (ceil_div(q_rows, 64), q_heads, 1), (128, 1, 1),
+                        args + [amax], shared_bytes=4 * 64 * (head_dim + 8) * 2, op=f"attention_{mask}_amax",
+                        algorithm="mma_streaming")
             return
         if (aligned and head_dim in FA_HEAD_DIMS and q_stride % 2 == 0 and o_stride % 2 == 0
                 and algorithm in ("auto", "fa")):
@@ -451,6 +459,20 @@ class RecipeBuilder:
             flags = ACT[act] | (FLAG_BIAS if bias else 0) | (FLAG_RESIDUAL if residual else 0) | \
                 (FLAG_OUT_F32 if out_f32 else 0) | (FLAG_SCALED if scale_a else 0)
             dummy = Arena(0)
+            # more 128 x TN output tiles than SMs: the persistent kernel (one CTA per SM walks the tiles, two
+            # accumulators in tensor memory, epilogue of one tile under the multiplication of the next)
+            m_tiles = ceil_div(M, 256)
+            TN = ceil_div(ceil_div(M, m_tiles), 16) * 16
+            tiles = ceil_div(N, 128) * m_tiles
+            if tactic in ("auto", "persistent") and (tiles >= 2 * SM_COUNT or tactic == "persistent"):
+                stage_bytes = 16384 + TN * 128
+                stages = max(2, min(12, TC_SMEM_BUDGET // stage_bytes))
+                self.launch("agi_gemm_tcq_e4m3", (min(tiles, SM_COUNT), 1, 1), (192, 1, 1),
+                            [x, w, y, bias or dummy, residual or dummy, scale_a or dummy, scale_w or dummy,
+                             Arena(STATUS_WORD), U32(M), U32(N), U32(K), U32(padded_token_rows(M)), U32(ldy or N),
+                             U32(flags), U32(TN), U32(stages)], shared_bytes=stages * stage_bytes + 1024,
+                            op="gemm_e4m3_packed", algorithm=f"tcgen05_persistent_128x{TN}_s{stages}")
+                return
             partial, counters = self._tc_scratch
             wide = t["rows"] == 256
             self.launch("agi_gemm_tcp_wide_e4m3" if wide else "agi_gemm_tcp_e4m3", (t["n_tiles"], t["m_tiles"], t["splits"]),

@@ -443,6 +443,62 @@ def test_gemm_group_packed_operands(tmp_path):
         assert ops.max_rel_err(got[f"y{i}"], want) < 1e-2, i
 
 
+@pytest.mark.parametrize("case", [(1024, 11008, 2048, "plain"), (600, 2560, 512, "bias_gelu_res"), (130, 300, 256, "bias"),
+                                  (1024, 1536, 1536, "res")], ids=lambda c: "-".join(map(str, c)))
+def test_gemm_persistent_packed(tmp_path, case):
+    """Persistent tcgen05 kernel (tile loop per CTA, double-buffered accumulators): more tiles than SMs, fewer
+    tiles than SMs, ragged edges, every epilogue."""
+    from aginfer_b200.recipes.layout import pack_kblock_swizzled, padded_token_rows
+    M, N, K, epi = case
+    x, wf = randn(M, K, seed=111), randn(N, K, seed=112, std=0.02)
+    bias = randn(N, seed=113, std=0.1) if "bias" in epi else None
+    res = randn(M, N, seed=114) if "res" in epi else None
+    act = "gelu_tanh" if "gelu" in epi else None
+    wq, ws = ops.quantize_e4m3(wf)
+    xq, xs = ops.quantize_e4m3(x)
+    want = ops.gemm(xq, wq, bias=bias, residual=res, act=act, scale_a=xs, scale_w=ws)
+    weights = {"w": pack_kblock_swizzled(wq), "w_scale": ws.reshape(())}
+    inputs = {"x": x}
+    if bias is not None:
+        weights["b"] = bias
+    if res is not None:
+        inputs["res"] = res
+
+    def body(r):
+        q, s = r.alloc(padded_token_rows(M) * K), r.alloc(4)
+        r.quantize_e4m3(Tensor("x"), q, s, M * K, packed=(M, K))
+        r.gemm(q, Weight("w"), Tensor("y"), M, N, K, dtype="e4m3", scale_a=s, scale_w=Weight("w_scale"),
+               bias=Weight("b") if bias is not None else None, residual=Tensor("res") if res is not None else None,
+               act=act, packed=True, tactic="persistent")
+        r.export_status(Tensor("status"))
+
+    got, _ = run_recipe(tmp_path, weights, inputs, {"y": (BF, (M, N)), "status": (torch.int32, (1,))}, body, repeats=3)
+    assert got["status"].item() == 0, hex(got["status"].item())
+    assert ops.max_rel_err(got["y"], want) < 1e-2
+
+
+@pytest.mark.parametrize("case", [(288, 16, 2, 128, "causal", 0), (512, 16, 16, 80, "block", 64)], ids=lambda c: "x".join(map(str, c)))
+def test_attention_that_folds_the_amax(tmp_path, case):
+    sq, hq, hkv, d, mask, arg = case
+    q, k, v = randn(sq, hq * d, seed=121), randn(sq, hkv * d, seed=122), randn(sq, hkv * d, seed=123)
+
+    def body(r):
+        o1, o2 = r.alloc(sq * hq * d * 2), r.alloc(sq * hq * d * 2)
+        kw = dict(q_rows=sq, kv_rows=sq, q_heads=hq, kv_heads=hkv, head_dim=d, q_stride=hq * d, k_stride=hkv * d,
+                  v_stride=hkv * d, o_stride=hq * d, mask=mask, mask_arg=arg)
+        amax = r.counter()
+        r.attention(Tensor("q"), Tensor("k"), Tensor("v"), o1, algorithm="fa", **kw)
+        r.quantize_e4m3(o1, Tensor("q_two_pass"), Tensor("s_two_pass"), sq * hq * d)
+        r.attention(Tensor("q"), Tensor("k"), Tensor("v"), o2, amax=amax, **kw)
+        r.quantize_e4m3(o2, Tensor("q_folded"), Tensor("s_folded"), sq * hq * d, amax=amax)
+
+    u8, f32 = (torch.uint8, (sq, hq * d)), (torch.float32, (1,))
+    got, _ = run_recipe(tmp_path, {}, {"q": q, "k": k, "v": v},
+                        {"q_two_pass": u8, "s_two_pass": f32, "q_folded": u8, "s_folded": f32}, body, repeats=2)
+    assert torch.equal(got["s_two_pass"], got["s_folded"]) and torch.equal(got["q_two_pass"], got["q_folded"])
+    assert got["s_folded"].item() > 0
+
+
 SKINNY_CASES = [
     (17, 1536, 1536, "bf16", "bias_gelu_res"), (17, 6144, 1536, "bf16", "bias_gelu"), (17, 1536, 6144, "bf16", "bias_res"),
     (4, 3072, 1536, "bf16", "bias"), (1, 1024, 64, "bf16", "bias"), (16, 1536, 32, "bf16", "bias"),

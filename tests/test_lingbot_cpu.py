@@ -30,7 +30,8 @@ def test_full_size_episode_compiles_to_a_plan():
     launches = recipe.plan()["shape_dispatch"][0]["launches"]
     kinds = collections.Counter(l["kernel"] for l in launches)
     assert kinds["agi_euler_step"] == cfg.steps
-    assert sum(n for k, n in kinds.items() if k.startswith("agi_attention_fa_bf16_d128")) == 28 + 18 * 10
+    assert kinds["agi_attention_fa_amax_bf16_d128"] == 28          # backbone: feeds an FP8 quantisation
+    assert kinds["agi_attention_fa_bf16_d128"] == 18 * 10          # expert: bf16 all the way
     compiled = planfmt.compile_execution_plan(recipe.plan(), CudaArch.SM100, weight_size=recipe.weight_bytes)
     assert compiled.input_names == ("pixels", "input_ids", "positions", "state", "noise")
     assert "actions" in compiled.output_names

@@ -58,6 +58,7 @@ def test_full_size_recipe_compiles_to_a_plan():
     ungrouped = qwen_vl.build_recipe(cfg, table(cfg), group=False).plan()["shape_dispatch"][0]["launches"]
     assert sum(1 for l in ungrouped if "e4m3" in l["kernel"] and "gemm" in l["kernel"]) == 5 * 32 + 2 + 7 * 36
     assert kinds["agi_quantize_e4m3_bf16"] == 4 * 32 + 2 + 4 * 36      # q/k/v and gate/up share one quantisation
+    assert kinds["agi_absmax_bf16"] == 1                               # only the merger's GELU output needs its own pass
     assert kinds["agi_patchify_f32_bf16"] == kinds["agi_unwindow_rows_bf16"] == kinds["agi_gather_rows_bf16"] == 1
     compiled = planfmt.compile_execution_plan(recipe.plan(), CudaArch.SM100, weight_size=recipe.weight_bytes)
     decoded = planfmt.decode_plan(compiled.data)
