@@ -461,9 +461,18 @@ class RecipeBuilder:
             dummy = Arena(0)
             # more 128 x TN output tiles than SMs: the persistent kernel (one CTA per SM walks the tiles, two
             # accumulators in tensor memory, epilogue of one tile under the multiplication of the next)
-            m_tiles = ceil_div(M, 256)
-            TN = ceil_div(ceil_div(M, m_tiles), 16) * 16
-            tiles = ceil_div(N, 128) * m_tiles
+            # token tile: the split of M whose tile count divides best over the SMs (rounds x bytes per tile;
+            # measured: a K block of 16 KB + TN * 128 B takes ~1 cycle per 40 bytes, the MMA 2 * TN cycles)
+            m_tiles, TN, tiles = 0, 0, 0
+            best_cost = None
+            for mt in range(ceil_div(M, 256), ceil_div(M, 256) + 4):
+                tn = ceil_div(ceil_div(M, mt), 16) * 16
+                if tn < 16:
+                    break
+                count = ceil_div(N, 128) * mt
+                cost = ceil_div(count, SM_COUNT) * max((16384 + tn * 128) / 40, 2 * tn)
+                if best_cost is None or cost < best_cost:
+                    best_cost, m_tiles, TN, tiles = cost, mt, tn, count
             if tactic in ("auto", "persistent") and (tiles >= 2 * SM_COUNT or tactic == "persistent"):
                 stage_bytes = 16384 + TN * 128
                 stages = max(2, min(12, TC_SMEM_BUDGET // stage_bytes))
