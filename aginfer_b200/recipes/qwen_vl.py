@@ -247,6 +247,10 @@ def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto", trace: bool 
         r.rmsnorm(x, Weight(gain), y, rows, cols, cfg.eps, amax=amax)
         quantize(y, q_rows or rows, q_cols or cols, amax=amax)
 
+    def attention_amax(head_dim: int):
+        """A counter for the attention kernel to leave max |o| in, for the head widths that have such a variant."""
+        return r.counter() if head_dim in (80, 128) else None
+
     def swiglu_quantize(gate, up, out, rows: int, cols: int):
         amax = r.counter()
         r.swiglu(gate, up, out, rows, cols, 2 * cols, amax=amax)
@@ -288,8 +292,8 @@ def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto", trace: bool 
         span = cfg.grid * cfg.grid if i in cfg.v_full_layers else cfg.window * cfg.window
         r.attention(qkv, qkv + VH * BF, qkv + 2 * VH * BF, attn, q_rows=P, kv_rows=P, q_heads=cfg.v_heads,
                     kv_heads=cfg.v_heads, head_dim=VD, q_stride=3 * VH, k_stride=3 * VH, v_stride=3 * VH, o_stride=VH,
-                    mask="block", mask_arg=span, amax=(a_max := r.counter()) if VD in (80, 128) else None)
-        quantize(attn, P, VH, amax=a_max if VD in (80, 128) else None)
+                    mask="block", mask_arg=span, amax=(a_max := attention_amax(VD)))
+        quantize(attn, P, VH, amax=a_max)
         linear_q(f"{b}.attn.proj", x2, P, VH, VH, residual=x)
         norm_quantize(x2, f"{b}.norm2.weight", normed, P, VH)
         group_q([(f"{b}.mlp.gate_proj", gate_up, VI, 2 * VI), (f"{b}.mlp.up_proj", gate_up + VI * BF, VI, 2 * VI)], P, VH)
@@ -327,8 +331,8 @@ def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto", trace: bool 
         r.mrope(k_cache, Tensor("positions"), S, cfg.kv_heads, D, cfg.kv_dim, cfg.theta, cfg.sections)
         r.attention(q_buf, k_cache, v_cache, att, q_rows=S, kv_rows=S, q_heads=cfg.heads, kv_heads=cfg.kv_heads,
                     head_dim=D, q_stride=cfg.q_dim, k_stride=cfg.kv_dim, v_stride=cfg.kv_dim, o_stride=cfg.q_dim,
-                    mask="causal", amax=(a_max := r.counter()) if D in (80, 128) else None)
-        quantize(att, S, cfg.q_dim, amax=a_max if D in (80, 128) else None)
+                    mask="causal", amax=(a_max := attention_amax(D)))
+        quantize(att, S, cfg.q_dim, amax=a_max)
         linear_q(f"{l}.self_attn.o_proj", h2, S, H, cfg.q_dim, residual=h)
         norm_quantize(h2, f"{l}.post_attention_layernorm.weight", hn, S, H)
         group_q([(f"{l}.mlp.gate_proj", gu, I, 2 * I), (f"{l}.mlp.up_proj", gu + I * BF, I, 2 * I)], S, H)
