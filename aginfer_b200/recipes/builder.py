@@ -473,7 +473,9 @@ class RecipeBuilder:
                 cost = ceil_div(count, SM_COUNT) * max((16384 + tn * 128) / 40, 2 * tn)
                 if best_cost is None or cost < best_cost:
                     best_cost, m_tiles, TN, tiles = cost, mt, tn, count
-            if tactic in ("auto", "persistent") and (tiles >= 2 * SM_COUNT or tactic == "persistent"):
+            # also preferred over K slices: measured at 2048 x 11008 the tile loop without slices (34-36 us at
+            # 288-1024 tokens) beats three slices with slabs (38-55 us)
+            if tactic in ("auto", "persistent") and (tiles >= 2 * SM_COUNT or t["splits"] > 1 or tactic == "persistent"):
                 stage_bytes = 16384 + TN * 128
                 stages = max(2, min(12, TC_SMEM_BUDGET // stage_bytes))
                 self.launch("agi_gemm_tcq_e4m3", (min(tiles, SM_COUNT), 1, 1), (192, 1, 1),
