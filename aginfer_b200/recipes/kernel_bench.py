@@ -19,7 +19,10 @@ D, T, MLP, LAYERS = 1536, 17, 6144, 16
 GEMM_SHAPES = {"gemm_q": (D, D), "gemm_fc1": (MLP, D), "gemm_fc2": (D, MLP),
                # the (N, K) grid of the FP8 GEMM sweep
                "gemm_2048x2048": (2048, 2048), "gemm_11008x2048": (11008, 2048), "gemm_2048x11008": (2048, 11008),
-               "gemm_2560x2048": (2560, 2048), "gemm_1536x1536": (1536, 1536), "gemm_6144x1536": (6144, 1536)}
+               "gemm_2560x2048": (2560, 2048), "gemm_1536x1536": (1536, 1536), "gemm_6144x1536": (6144, 1536),
+               # vision tower and 7B-shaped backbone
+               "gemm_3840x1280": (3840, 1280), "gemm_3456x1280": (3456, 1280), "gemm_1280x3456": (1280, 3456),
+               "gemm_3584x3584": (3584, 3584), "gemm_18944x3584": (18944, 3584), "gemm_3584x18944": (3584, 18944)}
 CASES = ("empty", "layernorm", "attn_self", "attn_cross", "attn_prefill", "attn_vision", *GEMM_SHAPES)
 
 
@@ -43,7 +46,7 @@ def build(case: str, tactic: str, reps: int, tokens: int, stages: int = 4, dtype
         weights["w_scale"] = torch.tensor(0.08 / 448, dtype=torch.float32)
     r = RecipeBuilder(describe(weights))
     r.begin_profile("default", [io("token", "I32", [1])], [io("status", "I32", [1])])
-    big = (max(tokens, 64) + 512) * 11008 * 2     # room for the padded rows of packed activations
+    big = (max(tokens, 64) + 512) * 18944 * 2     # room for the padded rows of packed activations
     x, y, scale_a = r.alloc(big), r.alloc(big), r.alloc(4)
     attn_bytes = max(tokens, 300) * 2048 * 2       # the widest attention operand of any case
     kbuf, vbuf, q = r.alloc(attn_bytes), r.alloc(attn_bytes), r.alloc(attn_bytes)

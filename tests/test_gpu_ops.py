@@ -384,8 +384,9 @@ PACKED_CASES = [(288, 2048, 2048, "bias"), (1024, 11008, 2048, "plain"), (288, 2
                 (130, 300, 256, "bias_gelu"), (512, 1280, 3456, "bias_res"), (17, 128, 128, "plain")]
 
 
+@pytest.mark.parametrize("tactic", ["auto", "tcgen05_plan"])     # auto may pick the persistent kernel; the plan never does
 @pytest.mark.parametrize("case", PACKED_CASES, ids=lambda c: "-".join(map(str, c)))
-def test_gemm_packed_operands(tmp_path, case):
+def test_gemm_packed_operands(tmp_path, case, tactic):
     """Bulk-copy tcgen05 GEMM: weights packed on the CPU (K-block-major, swizzled), activations quantised into
     the same layout on the device; same arithmetic as the row-major kernels."""
     from aginfer_b200.recipes.layout import pack_kblock_swizzled, padded_token_rows
@@ -409,7 +410,7 @@ def test_gemm_packed_operands(tmp_path, case):
         r.quantize_e4m3(Tensor("x"), q, s, M * K, packed=(M, K))
         r.gemm(q, Weight("w"), Tensor("y"), M, N, K, dtype="e4m3", scale_a=s, scale_w=Weight("w_scale"),
                bias=Weight("b") if bias is not None else None, residual=Tensor("res") if res is not None else None,
-               act=act, packed=True)
+               act=act, packed=True, tactic=tactic)
         r.export_status(Tensor("status"))
 
     got, _ = run_recipe(tmp_path, weights, inputs, {"y": (BF, (M, N)), "status": (torch.int32, (1,))}, body, repeats=3)
