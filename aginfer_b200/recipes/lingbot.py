@@ -164,8 +164,8 @@ def build_recipe(cfg: EpisodeConfig, weights, packed: bool = False, trace: bool 
                             v_stride=KV, o_stride=H, mask="none")
                 lin(att, f"{l}.self_attn.o_proj", seq2, T, H, H, residual=seq)
                 r.rmsnorm(seq2, Weight(f"{l}.post_attention_layernorm.weight"), hn, T, H, bb.eps)
-                r.fused_linear(hn, [(Weight(f"{l}.mlp.gate_proj.weight"), None, I), (Weight(f"{l}.mlp.up_proj.weight"), None, I)],
-                               gu, T, H)      # gate | up side by side in one weight-streaming launch
+                lin(hn, f"{l}.mlp.gate_proj", gu, T, I, H, ldy=2 * I)
+                lin(hn, f"{l}.mlp.up_proj", gu + I * BF, T, I, H, ldy=2 * I)
                 r.swiglu(gu, gu + I * BF, act, T, I, 2 * I)
                 lin(act, f"{l}.mlp.down_proj", seq, T, H, I, residual=seq2)
             r.rmsnorm(seq, Weight(f"{E}.norm.weight"), hn, T, H, bb.eps)
