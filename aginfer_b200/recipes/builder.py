@@ -506,6 +506,11 @@ class RecipeBuilder:
             # kernel (whole 128-byte K blocks); anything else falls back to the CUDA-core kernel.
             if M <= 64 and (K * elem) % 64 == 0 and aligned:
                 tactic = "stream"
+                # 33-64 tokens: the weight-streaming kernel needs 5-8 token tiles of accumulators per warp and
+                # slows down (50 tokens, 4096 x 1024: 18.8 us), while the tensor-core kernel with its K slices in
+                # a thread-block cluster does not care about the token count (8.6 us)
+                if M > 32 and tc_cluster_tiling(M, N, K, elem, dtype) is not None:
+                    tactic = "cluster"
             elif (K * elem) % 128 == 0 and aligned:
                 tactic = "tcgen05_plan" if M >= 128 else "tcgen05"
             else:

@@ -22,6 +22,8 @@ GEMM_SHAPES = {"gemm_q": (D, D), "gemm_fc1": (MLP, D), "gemm_fc2": (D, MLP),
                "gemm_2560x2048": (2560, 2048), "gemm_1536x1536": (1536, 1536), "gemm_6144x1536": (6144, 1536),
                # vision tower and 7B-shaped backbone
                "gemm_3840x1280": (3840, 1280), "gemm_3456x1280": (3456, 1280), "gemm_1280x3456": (1280, 3456),
+               "gemm_1024x1024": (1024, 1024), "gemm_512x1024": (512, 1024), "gemm_4096x1024": (4096, 1024),
+               "gemm_1024x4096": (1024, 4096),     # action expert
                "gemm_3584x3584": (3584, 3584), "gemm_18944x3584": (18944, 3584), "gemm_3584x18944": (3584, 18944)}
 CASES = ("empty", "layernorm", "attn_self", "attn_cross", "attn_prefill", "attn_vision", *GEMM_SHAPES)
 
