@@ -2,7 +2,8 @@
 // tower: 512 patch tokens, 80-wide heads, block-diagonal windows).  Streaming-softmax formulation on
 // warp-level MMAs:
 //
-//   * one block of 4 warps per (64 query rows, head); warp w owns rows 16w ... 16w + 15 and keeps its Q
+//   * one block of 1, 2 or 4 warps per (16, 32 or 64 query rows, head): fewer rows per block when the grid
+//     would otherwise leave most SMs idle; warp w owns rows 16w ... 16w + 15 and keeps its Q
 //     fragments, running row maxima / sums and the output accumulators in registers;
 //   * keys are visited in tiles of 64: K and V tiles are staged row-major in shared memory by 16-byte
 //     asynchronous copies, double-buffered so that tile i + 1 lands while tile i is multiplied;
@@ -13,14 +14,14 @@
 // Head width is a template parameter (16-element steps); grouped-query attention maps query head h to KV
 // head h / (q_heads / kv_heads).  Pitch of the shared tiles = head_dim + 8 elements: rows stay 16-byte
 // aligned and the eight rows of a fragment fall into different banks.
-// grid = (ceil(q_rows / 64), q_heads), block = 128, dynamic shared memory = 4 * 64 * (head_dim + 8) * 2.
+// grid = (ceil(q_rows / (16 * warps)), q_heads), block = 32 * warps, dynamic shared memory = 4 * 64 * (head_dim + 8) * 2.
 #pragma once
 
 #include "attention.cuh"
 
 namespace fa {
 
-constexpr unsigned kRowsPerBlock = 64, kKeyTile = 64;
+constexpr unsigned kKeyTile = 64;
 
 template <int HD16>
 __device__ __forceinline__ void attention_body(const bf16* q, const bf16* k, const bf16* v, bf16* o, unsigned q_rows,
@@ -33,8 +34,9 @@ __device__ __forceinline__ void attention_body(const bf16* q, const bf16* k, con
   grid_dependency_wait();
   const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
   const unsigned head = blockIdx.y, kv_head = head / (q_heads / kv_heads);
-  const unsigned row_base = blockIdx.x * kRowsPerBlock, warp_row = row_base + warp * 16;
-  const unsigned last_row = min(row_base + kRowsPerBlock, q_rows) - 1;
+  const unsigned rows_per_block = (blockDim.x >> 5) * 16;   // one 16-row MMA tile per warp; 1, 2 or 4 warps
+  const unsigned row_base = blockIdx.x * rows_per_block, warp_row = row_base + warp * 16;
+  const unsigned last_row = min(row_base + rows_per_block, q_rows) - 1;
 
   // keys this block of rows can see
   unsigned key_begin = 0, key_end = kv_rows;

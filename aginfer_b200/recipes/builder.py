@@ -412,16 +412,19 @@ class RecipeBuilder:
             self.launch("agi_attention_mma_bf16", (q_heads, ceil_div(q_rows, 16), 1), (256, 1, 1), args, shared_bytes=mma_smem,
                         op=f"attention_{mask}", algorithm="mma_key_split")
             return
+        # streaming tensor-core kernel: 4, 2 or 1 warps (64, 32 or 16 query rows) per block, the most rows that still
+        # give the grid about one block per SM
+        fa_warps = next((wp for wp in (4, 2, 1) if ceil_div(q_rows, 16 * wp) * q_heads >= 96), 1)
         if amax is not None:
             assert aligned and head_dim in (80, 128) and q_stride % 2 == 0 and o_stride % 2 == 0 and (q_rows > 64 or head_dim > 64)
-            self.launch(f"agi_attention_fa_amax_bf16_d{head_dim}", (ceil_div(q_rows, 64), q_heads, 1), (128, 1, 1),
+            self.launch(f"agi_attention_fa_amax_bf16_d{head_dim}", (ceil_div(q_rows, 16 * fa_warps), q_heads, 1), (32 * fa_warps, 1, 1),
                         args + [amax], shared_bytes=4 * 64 * (head_dim + 8) * 2, op=f"attention_{mask}_amax",
                         algorithm="mma_streaming")
             return
         if (aligned and head_dim in FA_HEAD_DIMS and q_stride % 2 == 0 and o_stride % 2 == 0
                 and algorithm in ("auto", "fa")):
             # many query rows: streaming softmax on tensor cores, 64 rows per block, keys in tiles of 64
-            self.launch(f"agi_attention_fa_bf16_d{head_dim}", (ceil_div(q_rows, 64), q_heads, 1), (128, 1, 1), args,
+            self.launch(f"agi_attention_fa_bf16_d{head_dim}", (ceil_div(q_rows, 16 * fa_warps), q_heads, 1), (32 * fa_warps, 1, 1), args,
                         shared_bytes=4 * 64 * (head_dim + 8) * 2, op=f"attention_{mask}", algorithm="mma_streaming")
             return
         if (aligned and q_rows <= 32 and head_dim <= 64 and rows_smem <= ATTN_SMEM_BUDGET
