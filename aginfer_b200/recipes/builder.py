@@ -16,6 +16,7 @@ use is recorded for ``tactics.json``.
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass, field
 from typing import Any, Mapping, Sequence
 
@@ -171,6 +172,10 @@ def tc_group_tiling(M: int, n_tiles: int, K: int, elem: int) -> dict[str, int]:
     return best
 
 
+# K >= ratio * N counts as K-heavy; 0 (default) disables the rule: in isolation the cluster kernel wins there
+# (17 tokens, 1536 x 6144: 9.4 us against 11.3 us), inside the action-head graph it does not (2.96 ms per chunk
+# against 2.93 ms), because the weight-streaming kernel starts its copies before the previous kernel has finished
+CLUSTER_K_RATIO = int(os.environ.get("AGI_CLUSTER_K_RATIO", "0"))
 FA_HEAD_DIMS = (48, 64, 80, 128)   # compiled widths of agi_attention_fa_bf16_d*
 
 
@@ -512,7 +517,8 @@ class RecipeBuilder:
                 # 33-64 tokens: the weight-streaming kernel needs 5-8 token tiles of accumulators per warp and
                 # slows down (50 tokens, 4096 x 1024: 18.8 us), while the tensor-core kernel with its K slices in
                 # a thread-block cluster does not care about the token count (8.6 us)
-                if M > 32 and tc_cluster_tiling(M, N, K, elem, dtype) is not None:
+                k_heavy = CLUSTER_K_RATIO > 0 and K >= CLUSTER_K_RATIO * N
+                if (M > 32 or k_heavy) and tc_cluster_tiling(M, N, K, elem, dtype) is not None:
                     tactic = "cluster"
             elif (K * elem) % 128 == 0 and aligned:
                 tactic = "tcgen05_plan" if M >= 128 else "tcgen05"
