@@ -53,8 +53,8 @@ def test_full_size_recipe_compiles_to_a_plan():
     kinds = collections.Counter(l["kernel"] for l in launches)
     # 5 linears per vision block, 2 merger, 7 per decoder layer, plus the bf16 patch embedding
     fp8 = sum(n for k, n in kinds.items() if k.startswith("agi_gemm_") and "e4m3" in k)
-    assert fp8 == 4 * 32 + 2 + 4 * 36                                  # gate|up and q|k|v share a launch each
-    assert kinds["agi_gemm_tc_e4m3_x3"] == 32 + 2 * 36
+    assert fp8 == 4 * 32 + 2 + 5 * 36                 # q|k|v share a launch; so do the vision tower's gate|up
+    assert kinds["agi_gemm_tc_e4m3_x3"] == 32 + 36
     ungrouped = qwen_vl.build_recipe(cfg, table(cfg), group=False).plan()["shape_dispatch"][0]["launches"]
     assert sum(1 for l in ungrouped if "e4m3" in l["kernel"] and "gemm" in l["kernel"]) == 5 * 32 + 2 + 7 * 36
     assert kinds["agi_quantize_e4m3_bf16"] == 4 * 32 + 2 + 4 * 36      # q/k/v and gate/up share one quantisation
