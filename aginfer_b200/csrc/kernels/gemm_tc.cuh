@@ -30,8 +30,10 @@
 
 #ifdef AGI_TRACE
 #define TC_STAMP(slot) do { if (blockIdx.x == 0 && blockIdx.z == 0 && lane == 0) status[(slot)] = (unsigned)clock64(); } while (0)
+#define TC_STAMP_ANY_SLICE(slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0) status[(slot)] = (unsigned)clock64(); } while (0)
 #else
 #define TC_STAMP(slot) do { } while (0)
+#define TC_STAMP_ANY_SLICE(slot) do { } while (0)
 #endif
 
 namespace tc {
@@ -255,6 +257,41 @@ __device__ __forceinline__ void store_features4(const float t4[4], unsigned m, u
 
 // grid = (ceil(N / 128), ceil(M / TN), splits), block = 160 threads,
 // dynamic shared memory = stages * (16384 + TN * 128) + 1024.
+// Split-K finish of one warp: token rows first, first + stride, ... of a tile, lane l owning four output features.
+// ROWS rows are summed per pass, over at most SLICES slabs each: every load of a pass is issued before the first
+// addition, so a pass costs one L2 round trip.  ROWS * SLICES = 32 float4 in flight per thread.
+template <int ROWS, int SLICES>
+__device__ __forceinline__ void finish_rows(const float* partial, size_t slab, unsigned splits, unsigned first,
+                                            unsigned stride, unsigned rows, unsigned m0, unsigned n, unsigned N,
+                                            unsigned Np, void* y, unsigned ldy, const bf16* bias, const bf16* residual,
+                                            float alpha, unsigned flags) {
+  for (unsigned i0 = first; i0 < rows; i0 += ROWS * stride) {
+    float4 part[ROWS][SLICES];
+#pragma unroll
+    for (int b = 0; b < ROWS; ++b) {
+      const unsigned i = i0 + b * stride;
+      if (i >= rows) continue;
+      const float4* cell = reinterpret_cast<const float4*>(partial + size_t(m0 + i) * Np + n);
+#pragma unroll
+      for (int z = 0; z < SLICES; ++z)
+        if (unsigned(z) < splits) part[b][z] = __ldcg(cell + z * slab);
+    }
+#pragma unroll
+    for (int b = 0; b < ROWS; ++b) {
+      const unsigned i = i0 + b * stride;
+      if (i >= rows) continue;
+      float4 total = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int z = 0; z < SLICES; ++z)   // slice order: the sum does not depend on which CTA arrived when
+        if (unsigned(z) < splits) {
+          total.x += part[b][z].x; total.y += part[b][z].y; total.z += part[b][z].z; total.w += part[b][z].w;
+        }
+      const float t4[4] = {total.x, total.y, total.z, total.w};
+      store_features4(t4, m0 + i, n, N, y, ldy, bias, residual, alpha, flags);
+    }
+  }
+}
+
 // kPacked: both operands are stored "K-block-major, swizzled" (see recipes/layout.py): the 128-byte K block kb
 // of row r lives at ((kb * rows_padded + r) * 128) with its 16-byte chunk c at position c ^ (r & 7), i.e. the
 // image of the shared-memory tile.  A ring slot is then filled by two bulk copies (16 KB of weights, TN * 128 B
@@ -532,6 +569,7 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
   __syncthreads();
   if (!last_flag) return;
   __threadfence();
+  if (warp == 0) TC_STAMP_ANY_SLICE(48);
   if (warp < 4) {
     // Warp w reduces token rows w, w + 4, ...; lane l owns output features n0 + 4l .. 4l + 3.  The
     // loads of one row's slabs are independent, so they are all in flight together; the additions
@@ -539,24 +577,13 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
     const float alpha = (flags & kFlagScaled) ? (*scale_a) * (*scale_w) : 1.f;
     const unsigned n = n0 + lane * 4;
     const unsigned rows = min(TN, M - m0);
-    for (unsigned i = warp; i < rows; i += 4) {
-      const unsigned m = m0 + i;
-      const float4* cell = reinterpret_cast<const float4*>(partial + size_t(m) * Np + n);
-      const size_t slab = size_t(M) * Np / 4;
-      float4 part[16];
-#pragma unroll
-      for (unsigned z = 0; z < 16; ++z)
-        if (z < splits) part[z] = __ldcg(cell + z * slab);
-      float4 total = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-      for (unsigned z = 0; z < 16; ++z)
-        if (z < splits) {
-          total.x += part[z].x; total.y += part[z].y; total.z += part[z].z; total.w += part[z].w;
-        }
-      const float t4[4] = {total.x, total.y, total.z, total.w};
-      store_features4(t4, m, n, N, y, ldy, bias, residual, alpha, flags);
-    }
+    const size_t slab = size_t(M) * Np / 4;
+    if (splits <= 2) finish_rows<16, 2>(partial, slab, splits, warp, 4, rows, m0, n, N, Np, y, ldy, bias, residual, alpha, flags);
+    else if (splits <= 4) finish_rows<8, 4>(partial, slab, splits, warp, 4, rows, m0, n, N, Np, y, ldy, bias, residual, alpha, flags);
+    else if (splits <= 8) finish_rows<4, 8>(partial, slab, splits, warp, 4, rows, m0, n, N, Np, y, ldy, bias, residual, alpha, flags);
+    else finish_rows<2, 16>(partial, slab, splits, warp, 4, rows, m0, n, N, Np, y, ldy, bias, residual, alpha, flags);
   }
+  if (warp == 0) TC_STAMP_ANY_SLICE(49);
   if (tid == 0) counters[tile] = 0;
 }
 

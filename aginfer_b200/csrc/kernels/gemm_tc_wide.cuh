@@ -243,25 +243,30 @@ __device__ __forceinline__ void gemm_wide_body(const uint8_t* x, const uint8_t* 
     const float alpha = (flags & kFlagScaled) ? (*scale_a) * (*scale_w) : 1.f;
     const unsigned rows = min(TN, M - m0);
     const size_t slab = size_t(M) * Np / 4;
-    for (unsigned i = warp; i < rows; i += kMmaWarp) {
-      const unsigned m = m0 + i;
+    // two token rows x two 128-row halves per pass: all their slab loads are in flight before the first sum
+    for (unsigned i0 = warp; i0 < rows; i0 += 2 * kMmaWarp) {
+      float4 part[4][8];
 #pragma unroll
-      for (unsigned h = 0; h < 2; ++h) {
-        const unsigned n = n0 + h * kTileN + lane * 4;
-        if (n >= N) continue;
-        const float4* cell = reinterpret_cast<const float4*>(partial + size_t(m) * Np + n);
-        float4 part[8];
+      for (unsigned u = 0; u < 4; ++u) {
+        const unsigned i = i0 + (u >> 1) * kMmaWarp, n = n0 + (u & 1) * kTileN + lane * 4;
+        if (i >= rows || n >= N) continue;
+        const float4* cell = reinterpret_cast<const float4*>(partial + size_t(m0 + i) * Np + n);
 #pragma unroll
         for (unsigned z = 0; z < 8; ++z)
-          if (z < splits) part[z] = __ldcg(cell + z * slab);
+          if (z < splits) part[u][z] = __ldcg(cell + z * slab);
+      }
+#pragma unroll
+      for (unsigned u = 0; u < 4; ++u) {
+        const unsigned i = i0 + (u >> 1) * kMmaWarp, n = n0 + (u & 1) * kTileN + lane * 4;
+        if (i >= rows || n >= N) continue;
         float4 total = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (unsigned z = 0; z < 8; ++z)
           if (z < splits) {
-            total.x += part[z].x; total.y += part[z].y; total.z += part[z].z; total.w += part[z].w;
+            total.x += part[u][z].x; total.y += part[u][z].y; total.z += part[u][z].z; total.w += part[u][z].w;
           }
         const float t4[4] = {total.x, total.y, total.z, total.w};
-        store_features4(t4, m, n, N, y, ldy, bias, residual, alpha, flags);
+        store_features4(t4, m0 + i, n, N, y, ldy, bias, residual, alpha, flags);
       }
     }
   }

@@ -473,7 +473,7 @@ class RecipeBuilder:
             # measured: a K block of 16 KB + TN * 128 B takes ~1 cycle per 40 bytes, the MMA 2 * TN cycles)
             m_tiles, TN, tiles = 0, 0, 0
             best_cost = None
-            for mt in range(ceil_div(M, 256), ceil_div(M, 256) + 4):
+            for mt in range(ceil_div(M, 256), ceil_div(M, 256) + int(os.environ.get("AGI_PERSIST_MT_SPAN", "4"))):
                 tn = ceil_div(ceil_div(M, mt), 16) * 16
                 if tn < 16:
                     break
@@ -481,9 +481,10 @@ class RecipeBuilder:
                 cost = ceil_div(count, SM_COUNT) * max((16384 + tn * 128) / 40, 2 * tn)
                 if best_cost is None or cost < best_cost:
                     best_cost, m_tiles, TN, tiles = cost, mt, tn, count
-            # also preferred over K slices: measured at 2048 x 11008 the tile loop without slices (34-36 us at
-            # 288-1024 tokens) beats three slices with slabs (38-55 us)
-            if tactic in ("auto", "persistent") and (tiles >= 2 * SM_COUNT or t["splits"] > 1 or tactic == "persistent"):
+            # also preferred over K slices while K is short (1280 x 3456, 512 tokens: 13.6 us against 18.6 us with two
+            # slices); with 86 or more K blocks per tile the slices win (2048 x 11008, 288 tokens: 24.8 us against 32.5 us)
+            short_k = t["splits"] > 1 and K // 128 <= 48
+            if tactic in ("auto", "persistent") and (tiles >= 2 * SM_COUNT or short_k or tactic == "persistent"):
                 stage_bytes = 16384 + TN * 128
                 stages = max(2, min(12, TC_SMEM_BUDGET // stage_bytes))
                 self.launch("agi_gemm_tcq_e4m3", (min(tiles, SM_COUNT), 1, 1), (192, 1, 1),
