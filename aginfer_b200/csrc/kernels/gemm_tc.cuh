@@ -496,6 +496,15 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
             else store_tokens16<false, false>(v, count, y, residual, offset, ldy, alpha, bias_v, flags);
           }
         }
+      } else if (kCluster == 1) {
+        // split-K slab: one base address per 16 tokens, rows Np apart
+        if (n < N && m0 + c0 < M) {
+          const unsigned count = min(16u, M - (m0 + c0));
+          float* cell = partial + (size_t(split) * M + m0 + c0) * Np + n;
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if (unsigned(i) < count) __stcg(cell + size_t(i) * Np, v[i]);
+        }
       } else if (n < N) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -507,7 +516,7 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
             const unsigned c = c0 + i, owner = c % kCluster;
             const unsigned cell = gather_base + (((split * gather_cols) + c / kCluster) * kTileN + warp * 32 + lane) * 4;
             store_peer_f32(peer_smem(cell, owner), v[i]);
-          } else __stcg(partial + (size_t(split) * M + m) * Np + n, v[i]);
+          }
         }
       }
     }
