@@ -500,6 +500,26 @@ def test_attention_that_folds_the_amax(tmp_path, case):
     assert got["s_folded"].item() > 0
 
 
+@pytest.mark.parametrize("shape", [(288, 2048), (50, 1280), (1, 128)], ids=lambda s: "x".join(map(str, s)))
+def test_quantize_e4m3_packed_layout_is_bit_exact(tmp_path, shape):
+    """Quantisation written in the packed operand layout: same bytes and scale as the oracle, at the addresses
+    recipes/layout.py defines (rows past M are padding and not compared)."""
+    from aginfer_b200.recipes.layout import padded_token_rows, unpack_kblock_swizzled
+    M, K = shape
+    x = randn(M, K, seed=131)
+    rp = padded_token_rows(M)
+
+    def body(r):
+        r.quantize_e4m3(Tensor("x"), Tensor("q"), Tensor("s"), M * K, packed=(M, K))
+
+    got, _ = run_recipe(tmp_path, {}, {"x": x}, {"q": (torch.uint8, (K // 128, rp, 128)), "s": (torch.float32, (1,))},
+                        body, repeats=2)
+    want_q, want_s = ops.quantize_e4m3(x)
+    assert got["s"].view(torch.int32).item() == want_s.reshape(1).view(torch.int32).item()
+    unpacked = unpack_kblock_swizzled(got["q"].view(torch.float8_e4m3fn), M)
+    assert torch.equal(unpacked.view(torch.uint8), want_q.view(torch.uint8))
+
+
 SKINNY_CASES = [
     (17, 1536, 1536, "bf16", "bias_gelu_res"), (17, 6144, 1536, "bf16", "bias_gelu"), (17, 1536, 6144, "bf16", "bias_res"),
     (4, 3072, 1536, "bf16", "bias"), (1, 1024, 64, "bf16", "bias"), (16, 1536, 32, "bf16", "bias"),
