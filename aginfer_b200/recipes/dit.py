@@ -165,8 +165,16 @@ def build_recipe(cfg: DitConfig = DitConfig(), weights: Mapping[str, tuple[str, 
     lin(t_sin, f"{P}.dit.timestep_embedder.linear_1", t_hid, S, D, cfg.time_dim, act="silu")
     lin(t_hid, f"{P}.dit.timestep_embedder.linear_2", temb, S, D, D)
     elementwise("agi_silu_bf16", [temb, temb_act, U32(S * D)], S * D, "silu")
-    for l in range(cfg.layers):
-        lin(temb_act, f"{P}.dit.blocks.{l}.norm1.linear", mods[l], S, 2 * D, D)
+    mod_jobs = [(Weight(f"{P}.dit.blocks.{l}.norm1.linear.weight"), Weight(f"{P}.dit.blocks.{l}.norm1.linear.bias"))
+                for l in range(cfg.layers)]
+    if batch_kv and (D * BF) % 128 == 0:
+        # the blocks' AdaLN projections share their input: 16 at a time as one tensor-core launch
+        # (mods[l] are equal-sized consecutive buffers, so block l's output starts l * S * 2D elements in)
+        for i in range(0, len(mod_jobs), 16):
+            r.gemm_batch(temb_act, mod_jobs[i:i + 16], mods[i], S, 2 * D, D, seg_stride=S * 2 * D)
+    else:
+        for l in range(cfg.layers):
+            lin(temb_act, f"{P}.dit.blocks.{l}.norm1.linear", mods[l], S, 2 * D, D)
     lin(temb_act, f"{P}.dit.norm_out.linear", mods[cfg.layers], S, 2 * D, D)
     elementwise("agi_bf16_to_f32", [Tensor("noise"), x_f32, U32(H * cfg.action_dim)], H * cfg.action_dim, "cast")
     elementwise("agi_copy_rows_bf16", [Tensor("noise"), x_bf, U32(H), U32(cfg.action_dim), U32(cfg.action_dim),

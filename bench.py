@@ -5,7 +5,7 @@
 Workload (``config.workload``): the GR00T-N1.5-shaped flow-matching DiT action head of the
 baseline's third configuration: 16 blocks x 1536, 17 tokens, cross-attention to 300 backbone
 tokens, 4 Euler steps, BF16 weights ~N(0, 0.02) seed 2, synthetic N(0, 1) inputs.  A "step" of
-this benchmark is one action chunk = one ``Session::Enqueue`` of the packaged recipe (520 kernel
+this benchmark is one action chunk = one ``Session::Enqueue`` of the packaged recipe (505 kernel
 launches replayed as one CUDA graph).  The real model's checkpoint is not available offline;
 seeded synthetic tensors of its shapes stand in.
 
