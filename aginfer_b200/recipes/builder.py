@@ -483,7 +483,8 @@ class RecipeBuilder:
                     best_cost, m_tiles, TN, tiles = cost, mt, tn, count
             # also preferred over K slices while K is short (1280 x 3456, 512 tokens: 13.6 us against 18.6 us with two
             # slices); with 86 or more K blocks per tile the slices win (2048 x 11008, 288 tokens: 24.8 us against 32.5 us)
-            short_k = t["splits"] > 1 and K // 128 <= 48
+            # ... unless there are enough tokens for the tile loop to cover the SMs by itself (1024 tokens: 35.8 us against 42.3 us)
+            short_k = t["splits"] > 1 and (K // 128 <= 48 or M >= 768)
             if tactic in ("auto", "persistent") and (tiles >= 2 * SM_COUNT or short_k or tactic == "persistent"):
                 stage_bytes = 16384 + TN * 128
                 stages = max(2, min(12, TC_SMEM_BUDGET // stage_bytes))
