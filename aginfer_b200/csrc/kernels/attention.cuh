@@ -29,7 +29,6 @@ extern "C" __global__ void __launch_bounds__(kAttnWarps * 32)
 agi_attention_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, unsigned q_rows, unsigned kv_rows,
                    unsigned q_heads, unsigned kv_heads, unsigned head_dim, unsigned q_stride, unsigned k_stride,
                    unsigned v_stride, unsigned o_stride, float scale, unsigned mask_mode, unsigned mask_arg) {
-  AGI_TRACE_KERNEL(4);
   __shared__ __align__(16) bf16 k_tile[kAttnChunk][kAttnMaxDim + 2];  // +2: odd word stride, conflict-free rows
   __shared__ __align__(16) bf16 v_tile[kAttnChunk][kAttnMaxDim];
   __shared__ float q_tile[kAttnWarps][kAttnMaxDim];
@@ -124,7 +123,6 @@ agi_attention_smem_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, un
                         unsigned q_heads, unsigned kv_heads, unsigned head_dim, unsigned q_stride, unsigned k_stride,
                         unsigned v_stride, unsigned o_stride, float scale, unsigned mask_mode, unsigned mask_arg,
                         unsigned span_max) {
-  AGI_TRACE_KERNEL(3);
   extern __shared__ __align__(16) unsigned char attn_smem[];
   grid_dependency_wait();
   const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -262,7 +260,6 @@ extern "C" __global__ void __launch_bounds__(kAttnWarps * 32)
 agi_attention_rows_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, unsigned q_rows, unsigned kv_rows,
                         unsigned q_heads, unsigned kv_heads, unsigned head_dim, unsigned q_stride, unsigned k_stride,
                         unsigned v_stride, unsigned o_stride, float scale, unsigned mask_mode, unsigned mask_arg) {
-  AGI_TRACE_KERNEL(9);
   extern __shared__ __align__(16) unsigned char attn_smem[];
   grid_dependency_wait();
   const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -407,7 +404,6 @@ extern "C" __global__ void __launch_bounds__(256)
 agi_attention_mma_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, unsigned q_rows, unsigned kv_rows,
                        unsigned q_heads, unsigned kv_heads, unsigned head_dim, unsigned q_stride, unsigned k_stride,
                        unsigned v_stride, unsigned o_stride, float scale, unsigned mask_mode, unsigned mask_arg) {
-  AGI_TRACE_KERNEL(10);
   extern __shared__ __align__(16) unsigned char attn_smem[];
   grid_dependency_wait();
   const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;

@@ -41,38 +41,6 @@ __device__ __forceinline__ void grid_dependency_wait() {
   asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
-// Launch timeline for tuning (-DAGI_TRACE only; compiled out of the shipped bundle): block (0,0,0) of every
-// kernel records the global timer when it starts and when it finishes.
-#ifdef AGI_TRACE
-__device__ unsigned g_trace_count;
-__device__ unsigned long long g_trace_stamps[2 * 8192];
-__device__ __forceinline__ unsigned long long global_timer() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-struct TraceScope {
-  unsigned slot;
-  __device__ __forceinline__ TraceScope(unsigned kernel_id) : slot(0xffffffffu) {
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) {
-      slot = atomicAdd(&g_trace_count, 1u) & 8191u;
-      g_trace_stamps[2 * slot] = (global_timer() << 8) | kernel_id;
-    }
-  }
-  __device__ __forceinline__ ~TraceScope() {
-    if (slot != 0xffffffffu) g_trace_stamps[2 * slot + 1] = global_timer();
-  }
-};
-#define AGI_TRACE_KERNEL(id) TraceScope agi_trace_scope(id)
-extern "C" __global__ void agi_trace_dump(unsigned long long* out, unsigned count) {
-  for (unsigned i = threadIdx.x; i < count; i += blockDim.x) out[i] = i == 0 ? g_trace_count : g_trace_stamps[i];
-  __syncthreads();
-  if (threadIdx.x == 0) g_trace_count = 0;
-}
-#else
-#define AGI_TRACE_KERNEL(id) do { } while (0)
-#endif
-
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -27,14 +27,6 @@
 #include "gemm_simt.cuh"    // gemm_store
 #include "gemm_skinny.cuh"  // mma16n8
 
-// Phase tracing for kernel tuning: with -DAGI_TRACE, CTA 0 stores SM clock stamps into the status area
-// (words 32..47: producer lane, words 48..63: consumer warp 0).  Compiled out of the shipped bundle.
-#ifdef AGI_TRACE
-#define AGI_STAMP(slot) do { if (blockIdx.x == 0 && lane == 0) status[(slot)] = (unsigned)clock64(); } while (0)
-#else
-#define AGI_STAMP(slot) do { } while (0)
-#endif
-
 namespace stream {
 
 // Consumer warps per CTA (plus one producer warp).  Four: the MMA phase is bound by the warp-level MMA
@@ -99,7 +91,6 @@ __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y
                                      const bf16* residual, const float* scale_a, const float* scale_w,
                                      unsigned* status, unsigned M, unsigned N, unsigned K, unsigned ldx, unsigned ldy,
                                      unsigned flags, unsigned rows, unsigned chunk_windows, const Extra extra = Extra()) {
-  AGI_TRACE_KERNEL(kLn ? 6 : 5);
   constexpr int kConsumerWarps = consumer_warps(NT);
   constexpr int kThreads = threads(NT);
   // dynamic shared memory: ring of slots (rows + M rows each), then the warps' partial tiles
@@ -164,7 +155,6 @@ __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y
     // ---------------- producer warp ----------------
     const size_t x_row = size_t(ldx) * elem;
     bool waited = false;
-    AGI_STAMP(32);
     for (unsigned c = 0; c < chunks; ++c) {
       const unsigned slot = c % kSlots, round = c / kSlots;
       const unsigned first = c * chunk_windows, count = min(chunk_windows, windows - first);
@@ -183,9 +173,7 @@ __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y
       if (!waited && (c + 1 == kSlots || c + 1 == chunks)) {
         // The weight copies of the first slots are in flight; only now wait for the previous kernel,
         // then fetch the activations it produced for those slots.
-        AGI_STAMP(33);
         grid_dependency_wait();
-        AGI_STAMP(34);
         waited = true;
         for (unsigned cc = 0; cc <= c; ++cc) {
           const unsigned f = cc * chunk_windows, n = min(chunk_windows, windows - f);
@@ -203,7 +191,6 @@ __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y
     }
     if (!waited) grid_dependency_wait();
     fetch_early();
-    AGI_STAMP(35);
   } else {
     // ---------------- consumer warps ----------------
     // Two accumulator sets (one per MMA of a 16-byte chunk) keep consecutive MMAs independent; fragments
@@ -237,9 +224,7 @@ __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y
           }
         }
       }
-      if (warp == 0 && c == 0) AGI_STAMP(48);
       bounded_wait(smem_u32(&full_bar[slot]), round & 1, status, kTimeoutFull | slot);
-      if (warp == 0 && c == 0) AGI_STAMP(49);
       if (c == 0) fetch_early();  // the slot landed, so the producer has passed the grid-dependency wait
       if (kLn && (flags & kFlagLayerNorm) && c == 0) {
         // Fused LayerNorm (whole rows are in this slot: the recipe only sets the flag when K is one chunk).
@@ -290,7 +275,6 @@ __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y
         }
         asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
       }
-      if (warp == 0 && c == 0) AGI_STAMP(50);
       const unsigned a_lo = base + g * pitch + t * 16, a_hi = a_lo + 8 * pitch;
       auto fetch = [&](int buf, unsigned win) {
         fa_lo[buf] = lds128(a_lo + win * 64);
@@ -335,10 +319,8 @@ __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y
       }
     }
   }
-  if (warp == 0) AGI_STAMP(51);
   grid_dependency_release();
   __syncthreads();
-  if (warp == 0) AGI_STAMP(52);
   const float alpha = (flags & kFlagScaled) ? (*scale_a) * (*scale_w) : 1.f;
   for (unsigned i = threadIdx.x; i < rows * M; i += kThreads) {
     const unsigned r = i % rows, m = i / rows;
@@ -360,7 +342,6 @@ __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y
       gemm_store(total, m, n, y, ldy, bias_seg - col0, residual, alpha, flags);
     }
   }
-  if (warp == 0) AGI_STAMP(53);
 }
 
 }  // namespace stream

@@ -28,14 +28,6 @@
 #include "common.cuh"
 #include "gemm_simt.cuh"  // gemm_store
 
-#ifdef AGI_TRACE
-#define TC_STAMP(slot) do { if (blockIdx.x == 0 && blockIdx.z == 0 && lane == 0) status[(slot)] = (unsigned)clock64(); } while (0)
-#define TC_STAMP_ANY_SLICE(slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0) status[(slot)] = (unsigned)clock64(); } while (0)
-#else
-#define TC_STAMP(slot) do { } while (0)
-#define TC_STAMP_ANY_SLICE(slot) do { } while (0)
-#endif
-
 namespace tc {
 
 constexpr unsigned kTileN = 128;          // weight rows per CTA (MMA M)
@@ -303,7 +295,6 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
                                           float* partial, unsigned* counters, unsigned* status, unsigned M,
                                           unsigned N, unsigned K, unsigned ldx, unsigned ldy, unsigned flags,
                                           unsigned TN, unsigned stages, unsigned tile_x = 0xffffffffu) {
-  AGI_TRACE_KERNEL(kCluster > 1 ? 8 : 7);
   extern __shared__ unsigned char dynamic_smem[];
   __shared__ __align__(8) unsigned long long full_bar[kMaxStages];
   __shared__ __align__(8) unsigned long long empty_bar[kMaxStages];
@@ -330,7 +321,6 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
   const unsigned Np = gridDim.x * kTileN;  // row stride of the split-K slabs: N rounded up to whole tiles
   if (stages > kMaxStages) stages = kMaxStages;
 
-  if (warp == 0) TC_STAMP(32);
   if (tid == 0) {
     for (unsigned s = 0; s < stages; ++s) {
       mbar_init(&full_bar[s], kPacked ? 1 : kProducers);
@@ -346,9 +336,7 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
   const unsigned tmem_base = tmem_slot;
   // Cluster split-K: every slice must be running (its shared memory live) before anyone writes into it.
   // Arrive now, wait only just before the first remote store: by then the barrier has long completed.
-  if (warp == 0) TC_STAMP(33);
   if (kCluster > 1) cluster_arrive();
-  if (warp == 0) TC_STAMP(34);
 
   // Weights do not depend on the previous kernel: the weight tiles of the first ring slots are requested
   // before the grid-dependency wait (they join the first commit group below).
@@ -394,7 +382,6 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
   }
 
   grid_dependency_wait();
-  if (warp == 0) TC_STAMP(35);
 
   if (kPacked && warp < 4) {
     // ---------------- warp 0 is the producer: two bulk copies per ring slot, issued by its lane 0 ----------------
@@ -418,9 +405,7 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
     for (unsigned i = 0; i < nkb + kLag; ++i) {
       if (i < nkb) {
         const unsigned s = i % stages, round = i / stages;
-        if (warp == 0 && i == 8) TC_STAMP(41);
         if (round > 0) mbar_wait(&empty_bar[s], (round - 1) & 1, status, kTimeoutEmpty | s);
-        if (warp == 0 && i == 8) TC_STAMP(42);
         if (i >= early) load_weights(i);
         const uint8_t* src = x_src + size_t(i) * kRowBytes;
         const unsigned dst = ring + s * stage_bytes + kATileBytes + dst_off;
@@ -429,10 +414,8 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
           if (j < b_rows) cp_async_16(dst + j * 2048, src + j * x_step);
       }
       cp_async_commit();  // an empty group past the end keeps the wait arithmetic uniform
-      if (warp == 0 && i == 8) TC_STAMP(43);
       if (i >= kLag) {
         cp_async_wait<kLag>();
-        if (warp == 0 && i == 8) TC_STAMP(44);
         fence_async_shared();
         mbar_arrive(&full_bar[(i - kLag) % stages]);
       }
@@ -442,10 +425,7 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
     const unsigned idesc = instr_descriptor<kFp8>(TN);
     for (unsigned i = 0; i < nkb; ++i) {
       const unsigned s = i % stages, round = i / stages;
-      if (i == 8) TC_STAMP(45);
       mbar_wait(&full_bar[s], round & 1, status, kTimeoutFull | s);
-      if (i == 0) TC_STAMP(46);
-      if (i == 8) TC_STAMP(47);
       tc_fence_after();
       if (lane == 0) {
         const unsigned a_base = ring + s * stage_bytes, b_base = a_base + kATileBytes;
@@ -463,10 +443,8 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
   }
 
   // ---------------- epilogue (warps 0-3: TMEM lanes 32 * warp ... +31) ----------------
-  if (warp == 0) TC_STAMP(36);   // producer loop finished
   if (warp < 4) {
     if (nkb > 0) mbar_wait(&accum_bar, 0, status, kTimeoutAccum);
-    if (warp == 0) TC_STAMP(37); // accumulator complete
     tc_fence_after();
     const unsigned n = n0 + warp * 32 + lane;
     const float alpha = (flags & kFlagScaled) ? (*scale_a) * (*scale_w) : 1.f;
@@ -522,7 +500,6 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
     }
     if (kCluster == 1 && splits > 1) __threadfence();  // partial sums ordered before this CTA's arrival count
     tc_fence_before();
-    if (warp == 0) TC_STAMP(38); // partial sums sent / stored
   }
   __syncthreads();
   if (warp == 4) {
@@ -545,7 +522,6 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
         early_res[j] = residual[size_t(m0 + split + j * kCluster) * ldy + n];
     cluster_arrive();
     cluster_wait();  // every slice's stores into this CTA's gather buffer are complete and visible
-    if (warp == 0) TC_STAMP(39);
     if (my_tokens != 0) {
       const float alpha = (flags & kFlagScaled) ? (*scale_a) * (*scale_w) : 1.f;
       const float* mine = reinterpret_cast<const float*>(dynamic_smem + (gather_base - smem_u32(dynamic_smem)));
@@ -564,7 +540,6 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
         else static_cast<bf16*>(y)[at] = __float2bfloat16_rn(r);
       }
     }
-    if (warp == 0) TC_STAMP(40);
     return;
   }
   if (splits == 1) return;
@@ -578,7 +553,6 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
   __syncthreads();
   if (!last_flag) return;
   __threadfence();
-  if (warp == 0) TC_STAMP_ANY_SLICE(48);
   if (warp < 4) {
     // Warp w reduces token rows w, w + 4, ...; lane l owns output features n0 + 4l .. 4l + 3.  The
     // loads of one row's slabs are independent, so they are all in flight together; the additions
@@ -592,7 +566,6 @@ __device__ __forceinline__ void gemm_body(const uint8_t* x, const uint8_t* w, vo
     else if (splits <= 8) finish_rows<4, 8>(partial, slab, splits, warp, 4, rows, m0, n, N, Np, y, ldy, bias, residual, alpha, flags);
     else finish_rows<2, 16>(partial, slab, splits, warp, 4, rows, m0, n, N, Np, y, ldy, bias, residual, alpha, flags);
   }
-  if (warp == 0) TC_STAMP_ANY_SLICE(49);
   if (tid == 0) counters[tile] = 0;
 }
 

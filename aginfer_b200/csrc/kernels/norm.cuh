@@ -48,7 +48,6 @@ __device__ __forceinline__ void rmsnorm_body(const bf16* x, const bf16* gain, bf
 
 extern "C" __global__ void agi_rmsnorm_bf16(const bf16* x, const bf16* gain, bf16* y, unsigned rows, unsigned cols,
                                              unsigned x_stride, unsigned y_stride, float eps) {
-  AGI_TRACE_KERNEL(2);
   rmsnorm_body<false>(x, gain, y, rows, cols, x_stride, y_stride, eps, nullptr);
 }
 
@@ -63,7 +62,6 @@ extern "C" __global__ void agi_rmsnorm_amax_bf16(const bf16* x, const bf16* gain
 extern "C" __global__ void agi_layernorm_bf16(const bf16* x, const bf16* scale, const bf16* shift, bf16* y,
                                                unsigned rows, unsigned cols, unsigned x_stride, unsigned y_stride,
                                                float eps, unsigned modulated) {
-  AGI_TRACE_KERNEL(1);
   __shared__ float scratch[32];
   grid_dependency_wait();
   const unsigned row = blockIdx.x;

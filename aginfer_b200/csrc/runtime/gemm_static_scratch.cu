@@ -21,7 +21,13 @@
 //
 // Set-up.  The first call on each device looks up the array's device address and raises the kernel's
 // dynamic shared-memory limit; both are one-time, per-device, synchronous host calls.  Make that first
-// call during start-up, outside any stream capture.
+// call during start-up, outside any stream capture.  The looked-up address is cached per device for the
+// life of the process: after cudaDeviceReset the cache is stale, so a process that resets a device must
+// not use this entry point on it again.
+//
+// Waits.  Every wait inside the kernel is bounded; one that runs out records a code in the first word of the
+// array and the kernel carries on, so the output is then wrong while the launch still succeeds.
+// agi_gemm_bf16_static_scratch_status copies that word to the caller (0 = every wait was satisfied).
 #include "aginfer_b200.h"
 
 #include "../kernels/gemm_tc.cuh"
@@ -29,6 +35,7 @@
 
 #include <cuda_runtime.h>
 
+#include <cstdint>
 #include <mutex>
 #include <string>
 
@@ -75,7 +82,9 @@ agi_status ScratchOnCurrentDevice(unsigned char** out) {
   return AGI_OK;
 }
 
-unsigned CeilDiv(unsigned a, unsigned b) { return (a + b - 1) / b; }
+std::uint64_t CeilDiv(std::uint64_t a, std::uint64_t b) { return (a + b - 1) / b; }
+
+bool Aligned(const void* p, std::uintptr_t to) { return (reinterpret_cast<std::uintptr_t>(p) & (to - 1)) == 0; }
 
 }  // namespace
 
@@ -83,27 +92,38 @@ extern "C" agi_status agi_gemm_bf16_static_scratch(const void* x, const void* w,
                                                    uint32_t N, uint32_t K, uint32_t splits, void* stream) {
   if (x == nullptr || w == nullptr || y == nullptr)
     return agi::RecordFailure(AGI_INVALID_ARGUMENT, "x, w and y must not be NULL");
-  if (M == 0 || N == 0 || K == 0 || (K * 2u) % 128u != 0)
+  // The kernel fetches X and W with 16-byte asynchronous copies: a base address off that boundary would be a
+  // misaligned-address fault on the GPU, so it is refused here, on the host.
+  if (!Aligned(x, 16) || !Aligned(w, 16))
+    return agi::RecordFailure(AGI_INVALID_ARGUMENT, "x and w must be 16-byte aligned device pointers");
+  if (!Aligned(y, 2) || !Aligned(bias, 2))
+    return agi::RecordFailure(AGI_INVALID_ARGUMENT, "y and bias must be 2-byte aligned (bf16) device pointers");
+  if (M == 0 || N == 0 || K == 0 || K % 64u != 0)
     return agi::RecordFailure(AGI_INVALID_ARGUMENT, "M, N, K must be positive and K a multiple of 64 elements");
+  // Grid limits of the launch: blockIdx.y walks token tiles of up to 256, blockIdx.x feature tiles of 128.
+  if (M > 256u * 65535u || K > 0x7fffffc0u)
+    return agi::RecordFailure(AGI_INVALID_ARGUMENT, "M or K is beyond what one launch can cover");
   // Same geometry rules as the packaged recipe: token tile a multiple of 16 up to 256, 128 rows of W per CTA.
-  const unsigned m_tiles = CeilDiv(M, 256), TN = CeilDiv(CeilDiv(M, m_tiles), 16) * 16;
-  const unsigned n_tiles = CeilDiv(N, 128), tiles = n_tiles * m_tiles, k_blocks = K * 2u / 128u;
+  const std::uint64_t m_tiles = CeilDiv(M, 256), TN = CeilDiv(CeilDiv(M, m_tiles), 16) * 16;
+  const std::uint64_t n_tiles = CeilDiv(N, 128), tiles = n_tiles * m_tiles, k_blocks = std::uint64_t(K) * 2 / 128;
   if (splits == 0) splits = 1;
   if (splits > 16 || splits > k_blocks)
     return agi::RecordFailure(AGI_INVALID_ARGUMENT, "splits must be between 1 and min(16, K / 64)");
-  const unsigned per = CeilDiv(k_blocks, splits);
-  splits = CeilDiv(k_blocks, per);
-  const size_t need = splits > 1 ? size_t(splits) * M * n_tiles * 128 * sizeof(float) : 0;
-  if (tiles > kMaxTiles || need > kPartialBytes)
+  const std::uint64_t per = CeilDiv(k_blocks, splits);
+  splits = static_cast<uint32_t>(CeilDiv(k_blocks, per));
+  // One K slice needs neither partial tiles nor arrival counters.
+  const std::uint64_t need = splits > 1 ? std::uint64_t(splits) * M * n_tiles * 128 * sizeof(float) : 0;
+  if (splits > 1 && (tiles > kMaxTiles || need > kPartialBytes))
     return agi::RecordFailure(
         AGI_INVALID_ARGUMENT,
         "shape needs " + std::to_string(need) + " bytes of split-K scratch and " + std::to_string(tiles) +
             " tile counters; the built-in array holds " + std::to_string(kPartialBytes) + " bytes and " +
             std::to_string(kMaxTiles) + " counters (use fewer splits, or the session path)");
-  const unsigned stage_bytes = 16384 + TN * 128;
+  const unsigned stage_bytes = 16384 + unsigned(TN) * 128;
+  const unsigned depth = per < 3 ? 3u : unsigned(per > 12 ? 12 : per);
   unsigned stages = kSmemBudget / stage_bytes;
   if (stages > 12) stages = 12;
-  if (stages > (per < 3 ? 3u : per)) stages = per < 3 ? 3u : per;
+  if (stages > depth) stages = depth;
   if (stages < 3) stages = 3;
   const unsigned shared_bytes = stages * stage_bytes + 1024;
 
@@ -118,9 +138,19 @@ extern "C" agi_status agi_gemm_bf16_static_scratch(const void* x, const void* w,
     return s;
   const unsigned flags = bias != nullptr ? kFlagBias : 0u;
   const bf16* dummy = static_cast<const bf16*>(y);  // never dereferenced when its flag is off
-  agi_gemm_tc_bf16<<<dim3(n_tiles, m_tiles, splits), tc::kThreads, shared_bytes, cu_stream>>>(
+  agi_gemm_tc_bf16<<<dim3(unsigned(n_tiles), unsigned(m_tiles), splits), tc::kThreads, shared_bytes, cu_stream>>>(
       static_cast<const bf16*>(x), static_cast<const bf16*>(w), y, bias != nullptr ? static_cast<const bf16*>(bias) : dummy,
       dummy, reinterpret_cast<const float*>(status), reinterpret_cast<const float*>(status), partial, counters, status,
-      M, N, K, K, N, flags, TN, stages);
+      M, N, K, K, N, flags, unsigned(TN), stages);
   return Cuda(cudaGetLastError(), "agi_gemm_tc_bf16 launch");
+}
+
+extern "C" agi_status agi_gemm_bf16_static_scratch_status(uint32_t* out, void* stream) {
+  if (out == nullptr || !Aligned(out, 4))
+    return agi::RecordFailure(AGI_INVALID_ARGUMENT, "out must be a 4-byte aligned device or pinned host word");
+  unsigned char* scratch = nullptr;
+  if (agi_status s = ScratchOnCurrentDevice(&scratch)) return s;
+  // Ordered on `stream` behind the GEMM whose waits it reports; copies four bytes, allocates nothing.
+  return Cuda(cudaMemcpyAsync(out, scratch, sizeof(uint32_t), cudaMemcpyDefault, static_cast<cudaStream_t>(stream)),
+              "cudaMemcpyAsync");
 }

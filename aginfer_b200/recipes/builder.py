@@ -16,7 +16,6 @@ use is recorded for ``tactics.json``.
 from __future__ import annotations
 
 import math
-import os
 from dataclasses import dataclass, field
 from typing import Any, Mapping, Sequence
 
@@ -87,7 +86,7 @@ ATTN_SMEM_BUDGET = 200 * 1024    # dynamic shared memory of the keys-in-shared-m
 USE_SLAB_COPIES = False
 # 16 weight rows per CTA use the whole 16-row MMA tile and halve the activation re-reads per weight byte; 8 rows
 # give twice as many CTAs.  16 is chosen when it still yields at least this many CTAs.
-STREAM_MIN_CTAS_FOR_16_ROWS = int(__import__('os').environ.get('AGI_STREAM_MIN16', SM_COUNT))
+STREAM_MIN_CTAS_FOR_16_ROWS = SM_COUNT
 STREAM_SM_BYTES = 220 * 1024     # shared memory the bulk-stream GEMM CTAs of one SM may use together
 STREAM_CTA_BYTES = 110 * 1024    # and the most a single CTA takes (two CTAs per SM keep one draining while one fills)
 
@@ -175,7 +174,8 @@ def tc_group_tiling(M: int, n_tiles: int, K: int, elem: int) -> dict[str, int]:
 # K >= ratio * N counts as K-heavy; 0 (default) disables the rule: in isolation the cluster kernel wins there
 # (17 tokens, 1536 x 6144: 9.4 us against 11.3 us), inside the action-head graph it does not (2.96 ms per chunk
 # against 2.93 ms), because the weight-streaming kernel starts its copies before the previous kernel has finished
-CLUSTER_K_RATIO = int(os.environ.get("AGI_CLUSTER_K_RATIO", "0"))
+CLUSTER_K_RATIO = 0
+PERSIST_TOKEN_SPLITS = 4             # token-tile counts the persistent GEMM's planner tries beyond the minimum
 FA_HEAD_DIMS = (48, 64, 80, 128)   # compiled widths of agi_attention_fa_bf16_d*
 
 
@@ -473,7 +473,7 @@ class RecipeBuilder:
             # measured: a K block of 16 KB + TN * 128 B takes ~1 cycle per 40 bytes, the MMA 2 * TN cycles)
             m_tiles, TN, tiles = 0, 0, 0
             best_cost = None
-            for mt in range(ceil_div(M, 256), ceil_div(M, 256) + int(os.environ.get("AGI_PERSIST_MT_SPAN", "4"))):
+            for mt in range(ceil_div(M, 256), ceil_div(M, 256) + PERSIST_TOKEN_SPLITS):
                 tn = ceil_div(ceil_div(M, mt), 16) * 16
                 if tn < 16:
                     break

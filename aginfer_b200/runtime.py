@@ -81,6 +81,7 @@ EXPORTS = {
     "agi_session_get_stats": (C.c_int, [C.c_void_p, C.POINTER(_Stats)]),
     "agi_gemm_bf16_static_scratch": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32,
                                                 C.c_uint32, C.c_uint32, C.c_void_p]),
+    "agi_gemm_bf16_static_scratch_status": (C.c_int, [C.c_void_p, C.c_void_p]),
     "agi_sha256": (C.c_int, [C.c_void_p, C.c_size_t, C.c_int, C.POINTER(C.c_uint8)]),
 }
 
@@ -299,3 +300,9 @@ def gemm_bf16_static_scratch(x_ptr: int, w_ptr: int, y_ptr: int, bias_ptr: int |
     _check(load_library().agi_gemm_bf16_static_scratch(C.c_void_p(x_ptr), C.c_void_p(w_ptr), C.c_void_p(y_ptr),
                                                        C.c_void_p(bias_ptr) if bias_ptr else None, M, N, K, splits,
                                                        C.c_void_p(stream)))
+
+
+def gemm_bf16_static_scratch_status(out_ptr: int, stream: int = 0) -> None:
+    """``agi_gemm_bf16_static_scratch_status``: copy the wait-status word of the last static-scratch GEMM
+    into the caller's 4-byte device (or pinned host) word at ``out_ptr``, ordered on ``stream``."""
+    _check(load_library().agi_gemm_bf16_static_scratch_status(C.c_void_p(out_ptr), C.c_void_p(stream)))

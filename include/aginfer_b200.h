@@ -167,10 +167,19 @@ AGI_API agi_status agi_session_get_stats(const agi_session* session, agi_session
  * number of K slices.  Limit: splits * M * roundup(N, 128) * 4 bytes <= 8 MiB and at most 1024 output
  * tiles, otherwise AGI_INVALID_ARGUMENT.  The array is shared by every call on a device and keeps the
  * last call's contents (what must be zero is cleared on `stream` first); calls that overlap on one GPU
- * race.  The first call on each device performs one-time synchronous set-up (symbol address lookup,
- * kernel attribute): make it during start-up, before any stream capture. */
+ * race.  `x` and `w` must be 16-byte aligned (the kernel fetches them with 16-byte copies), `y` and `bias`
+ * 2-byte aligned; anything else is refused with AGI_INVALID_ARGUMENT before a launch.  The first call on
+ * each device performs one-time synchronous set-up (symbol address lookup, kernel attribute): make it
+ * during start-up, before any stream capture; the looked-up address is cached for the life of the
+ * process, so do not use the entry point on a device after cudaDeviceReset. */
 AGI_API agi_status agi_gemm_bf16_static_scratch(const void* x, const void* w, void* y, const void* bias, uint32_t M,
                                                 uint32_t N, uint32_t K, uint32_t splits, void* stream);
+/* No counterpart in the reference.  Copies the wait-status word of the static-scratch GEMM (first word of
+ * the built-in array; 0 = every bounded wait inside the kernel was satisfied, anything else = the output
+ * of the last call on this device is not to be trusted) into `out`, a 4-byte aligned device or pinned
+ * host word, with one cudaMemcpyAsync on `stream`: enqueue it behind the GEMM it reports on.  Allocates
+ * nothing. */
+AGI_API agi_status agi_gemm_bf16_static_scratch_status(uint32_t* out, void* stream);
 
 /* SHA-256 of a buffer with the library's hasher (test hook; `portable` != 0 forces the
  * non-accelerated block function). Role of cpp/sha256.cc:58-103. */

@@ -20,7 +20,9 @@ from pathlib import Path
 
 
 def main() -> int:
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_format_golden.py /path/to/AgInfer")
+    ref = Path(sys.argv[1])
     sys.path[:0] = [str(ref / "src"), str(ref)]
     from aginfer.aim import AimWriter, VariantPayload
     from aginfer.checkpoint import load_checkpoint, pack_weights

@@ -15,6 +15,7 @@ import torch
 
 from aginfer_b200 import runtime as rt
 from aginfer_b200.recipes import Tensor, Weight
+from oracle import ops
 from tests.gpu_util import run_recipe
 
 pytestmark = pytest.mark.gpu
@@ -29,24 +30,36 @@ def reference_through_session(tmp_path, x, w, bias, splits):
     return got["y"]
 
 
-@pytest.mark.parametrize("M,N,K,splits", [(17, 1536, 1536, 12), (288, 2560, 2048, 2), (50, 1000, 4096, 1)])
+@pytest.mark.parametrize("M,N,K,splits", [(17, 1536, 1536, 12), (288, 2560, 2048, 2), (50, 1000, 4096, 1),
+                                          (33, 1000, 1024, 4)])
 def test_static_scratch_gemm_equals_session_gemm_twice(tmp_path, M, N, K, splits):
     g = torch.Generator().manual_seed(7)
     x = torch.randn(M, K, generator=g).to(BF)
     w = (torch.randn(N, K, generator=g) * 0.02).to(BF)
     bias = (torch.randn(N, generator=g) * 0.1).to(BF)
     want = reference_through_session(tmp_path, x, w, bias, splits)
+    oracle = ops.gemm(x, w, bias=bias)
 
     dx, dw, db = x.cuda(), w.cuda(), bias.cuda()
+    status = torch.full((1,), -1, dtype=torch.int32, device="cuda")
     stream = torch.cuda.Stream()
+    free_before = None
     for attempt in range(2):
         dy = torch.full((M, N), float("nan"), dtype=BF, device="cuda")
         torch.cuda.synchronize()
+        if attempt == 1:                     # the first call did the one-time set-up; this one must hold nothing new
+            free_before = torch.cuda.mem_get_info()[0]
         rt.gemm_bf16_static_scratch(dx.data_ptr(), dw.data_ptr(), dy.data_ptr(), db.data_ptr(), M, N, K, splits,
                                     stream.cuda_stream)
+        rt.gemm_bf16_static_scratch_status(status.data_ptr(), stream.cuda_stream)
         stream.synchronize()
+        if attempt == 1:
+            assert torch.cuda.mem_get_info()[0] == free_before, "a warmed call changed the device's free memory"
+        assert int(status.item()) == 0, "a bounded wait inside the kernel ran out"
         # same kernel, same tiling, slice-ordered summation: the two paths agree bit for bit
         assert torch.equal(dy.cpu(), want), f"call {attempt + 1} differs from the session path"
+        # and both sit on the CPU oracle of the GEMM
+        assert ops.max_rel_err(dy.cpu(), oracle) < 1e-2
 
 
 def test_static_scratch_gemm_refuses_what_does_not_fit():
@@ -58,6 +71,13 @@ def test_static_scratch_gemm_refuses_what_does_not_fit():
     assert caught.value.name == "INVALID_ARGUMENT"
     with pytest.raises(rt.RuntimeStatusError, match="multiple of 64"):
         rt.gemm_bf16_static_scratch(x.data_ptr(), w.data_ptr(), y.data_ptr(), None, 4, 4, 100, 1)
+    # operands the kernel would fetch with misaligned 16-byte copies are refused on the host, never launched
+    for bad_x, bad_w in ((2, 0), (0, 8)):
+        with pytest.raises(rt.RuntimeStatusError, match="16-byte aligned") as caught:
+            rt.gemm_bf16_static_scratch(x.data_ptr() + bad_x, w.data_ptr() + bad_w, y.data_ptr(), None, 16, 128, 64, 1)
+        assert caught.value.name == "INVALID_ARGUMENT"
+    with pytest.raises(rt.RuntimeStatusError, match="2-byte aligned"):
+        rt.gemm_bf16_static_scratch(x.data_ptr(), w.data_ptr(), y.data_ptr() + 1, None, 16, 128, 64, 1)
     # one slice needs no scratch at all, so the same shape is accepted
     rt.gemm_bf16_static_scratch(x.data_ptr(), w.data_ptr(), y.data_ptr(), None, 1024, 4096, 2048, 1)
     torch.cuda.synchronize()
