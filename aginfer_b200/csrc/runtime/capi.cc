@@ -202,7 +202,7 @@ agi_status agi_session_get_required_workspace(const agi_session* session, const 
 }
 
 agi_status agi_session_enqueue(agi_session* session, const agi_tensor_view* inputs, size_t input_count,
-                               const agi_tensor_view* outputs, size_t output_count, const agi_run_options*,
+                               const agi_tensor_view* outputs, size_t output_count, const agi_run_options* options,
                                void* stream) {
   if (session == nullptr) return Null("session");
   if ((inputs == nullptr && input_count != 0) || (outputs == nullptr && output_count != 0)) return Null("views");
@@ -211,8 +211,17 @@ agi_status agi_session_enqueue(agi_session* session, const agi_tensor_view* inpu
     const agi_tensor_view& v = i < input_count ? inputs[i] : outputs[i - input_count];
     args[i] = agi::TensorArg{v.name, v.dtype, v.location, v.rank, v.shape, v.stride, v.data, v.byte_size};
   }
+  agi::RunSelect select;
+  agi::TensorArg noise;
+  if (options != nullptr) {
+    select.denoising_steps = options->denoising_steps;
+    if (const agi_tensor_view* v = options->initial_noise_override) {
+      noise = agi::TensorArg{v->name, v->dtype, v->location, v->rank, v->shape, v->stride, v->data, v->byte_size};
+      select.noise_override = &noise;
+    }
+  }
   return Done(session->impl->Enqueue(args.data(), input_count, args.data() + input_count, output_count,
-                                     static_cast<CUstream>(stream)));
+                                     static_cast<CUstream>(stream), select));
 }
 
 agi_status agi_session_get_stats(const agi_session* session, agi_session_stats* out) {
@@ -220,7 +229,7 @@ agi_status agi_session_get_stats(const agi_session* session, agi_session_stats* 
   if (out == nullptr) return Null("out");
   const agi::SessionStats& s = session->impl->stats();
   *out = agi_session_stats{s.enqueues, s.kernel_launches, s.graph_launches, s.graphs_built,
-                           session->impl->profile().launch_count, s.upload_seconds};
+                           session->impl->active_profile().launch_count, s.upload_seconds};
   return AGI_OK;
 }
 

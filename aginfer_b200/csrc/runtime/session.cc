@@ -107,11 +107,9 @@ Status Session::Create(const RuntimeOptions& rt, const Package& package, const s
   if (s->profile_ == nullptr)
     return Status(kInvalidArgument, "profile is not present in the static execution plan: " + profile);
   s->bound_.assign(s->profile_->tensor_count, nullptr);
-  std::uint32_t widest = 0;
-  for (std::uint32_t l = 0; l < s->profile_->launch_count; ++l)
-    widest = std::max(widest, s->plan_.launches[s->profile_->first_launch + l].argument_count);
-  s->slots_.resize(widest);
-  s->params_.resize(widest);
+  s->states_.push_back(std::make_unique<ProfileState>());
+  s->states_[0]->profile = s->profile_;
+  s->active_ = s->states_[0].get();
   *out = std::move(s);
   return {};
 }
@@ -119,8 +117,9 @@ Status Session::Create(const RuntimeOptions& rt, const Package& package, const s
 Session::~Session() {
   if (cu_ == nullptr || context_ == nullptr) return;
   cu_->cuCtxSetCurrent(context_);
-  for (CachedGraph& g : graphs_)
-    if (g.exec != nullptr) cu_->cuGraphExecDestroy(g.exec);
+  for (auto& state : states_)
+    for (CachedGraph& g : state->graphs)
+      if (g.exec != nullptr) cu_->cuGraphExecDestroy(g.exec);
   if (workspace_ != 0) cu_->cuMemFree(workspace_);
   if (arena_ != 0) cu_->cuMemFree(arena_);
   if (weights_ != 0) cu_->cuMemFree(weights_);
@@ -250,14 +249,62 @@ Status Session::Prepare() {
   if (workspace_ == 0 && workspace_bytes != 0)
     AGI_RETURN_IF_ERROR(cu_->Check(cu_->cuMemAlloc(&workspace_, static_cast<std::size_t>(workspace_bytes)), "cuMemAlloc", kOutOfMemory));
 
+  prepared_ = true;
+  return {};
+}
+
+// Select the profile an Enqueue runs: the session's own, or its sibling for another number of denoising steps.
+// A sibling must take and return exactly the tensors of the session's profile.
+Status Session::Select(std::uint32_t denoising_steps) {
+  if (denoising_steps == 0) {
+    active_ = states_[0].get();
+    return {};
+  }
+  const std::string name = std::string(plan_.Text(profile_->name)) + "/steps=" + std::to_string(denoising_steps);
+  for (auto& state : states_)
+    if (plan_.Text(state->profile->name) == name) {
+      active_ = state.get();
+      return {};
+    }
+  const wire::Profile* found = plan_.Find(name);
+  if (found == nullptr)
+    return Status(kInvalidArgument, "no recipe for " + std::to_string(denoising_steps) +
+                                        " denoising steps in the static execution plan (profile " + name + ")");
+  bool same = found->tensor_count == profile_->tensor_count;
+  for (std::uint32_t i = 0; same && i < found->tensor_count; ++i) {
+    const wire::Tensor& a = plan_.tensors[found->first_tensor + i];
+    const wire::Tensor& b = plan_.tensors[profile_->first_tensor + i];
+    same = plan_.Text(a.name) == plan_.Text(b.name) && a.dtype == b.dtype && a.location == b.location &&
+           a.io_kind == b.io_kind && a.rank == b.rank && a.byte_size == b.byte_size &&
+           std::memcmp(a.shape, b.shape, sizeof(a.shape)) == 0 && std::memcmp(a.stride, b.stride, sizeof(a.stride)) == 0;
+  }
+  if (!same) return Status(kCorruptPackage, "profile " + name + " does not have the tensors of the session's profile");
+  states_.push_back(std::make_unique<ProfileState>());
+  states_.back()->profile = found;
+  active_ = states_.back().get();
+  return {};
+}
+
+Status Session::Resolve() {
+  ProfileState& state = *active_;
+  if (state.resolved) return {};
+  const wire::Profile* profile = state.profile;
+  std::uint32_t widest = 0;
+  for (std::uint32_t l = 0; l < profile->launch_count; ++l)
+    widest = std::max(widest, plan_.launches[profile->first_launch + l].argument_count);
+  if (slots_.size() < widest) {
+    slots_.resize(widest);
+    params_.resize(widest);
+  }
   // Resolve each distinct kernel once; a function's dynamic shared-memory limit is a property of the
   // function, so it is raised to the largest request any launch of the profile makes.
-  functions_.clear();
-  functions_.reserve(profile_->launch_count);
+  state.functions.clear();
+  state.functions.reserve(profile->launch_count);
+  state.cooperative.clear();
   std::vector<std::pair<std::uint32_t, CUfunction>> resolved;      // name offset -> function
   std::vector<std::uint32_t> shared_need;
-  for (std::uint32_t l = 0; l < profile_->launch_count; ++l) {
-    const wire::Launch& launch = plan_.launches[profile_->first_launch + l];
+  for (std::uint32_t l = 0; l < profile->launch_count; ++l) {
+    const wire::Launch& launch = plan_.launches[profile->first_launch + l];
     std::size_t slot = 0;
     while (slot < resolved.size() && resolved[slot].first != launch.kernel) ++slot;
     if (slot == resolved.size()) {
@@ -268,7 +315,8 @@ Status Session::Prepare() {
       shared_need.push_back(0);
     }
     shared_need[slot] = std::max(shared_need[slot], launch.shared_bytes);
-    functions_.push_back(resolved[slot].second);
+    state.functions.push_back(resolved[slot].second);
+    state.cooperative.push_back(plan_.Text(launch.kernel).rfind("agi_coop_", 0) == 0);
   }
   for (std::size_t slot = 0; slot < resolved.size(); ++slot) {
     // Ask for the same (largest) shared-memory carve-out for every kernel of the recipe: consecutive launches
@@ -279,23 +327,26 @@ Status Session::Prepare() {
     int static_bytes = 0;
     cu_->cuFuncGetAttribute(&static_bytes, CU_FUNC_ATTRIBUTE_SHARED_SIZE_BYTES, resolved[slot].second);
     if (shared_need[slot] + static_cast<std::uint32_t>(static_bytes) <= kStaticSharedLimit) continue;
+    int granted = 0;   // another profile of this session may already have raised the limit further
+    cu_->cuFuncGetAttribute(&granted, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, resolved[slot].second);
+    if (granted >= static_cast<int>(shared_need[slot])) continue;
     const std::string name(plan_.Text(resolved[slot].first));
     AGI_RETURN_IF_ERROR(cu_->Check(cu_->cuFuncSetAttribute(resolved[slot].second, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES,
                                                            static_cast<int>(shared_need[slot])),
                                    "cuFuncSetAttribute(" + name + ")"));
   }
-  prepared_ = true;
+  state.resolved = true;
   return {};
 }
 
 Status Session::Issue(CUstream stream) {
-  for (std::uint32_t l = 0; l < profile_->launch_count; ++l) {
-    const wire::Launch& launch = plan_.launches[profile_->first_launch + l];
+  for (std::uint32_t l = 0; l < active_->profile->launch_count; ++l) {
+    const wire::Launch& launch = plan_.launches[active_->profile->first_launch + l];
     for (std::uint32_t a = 0; a < launch.argument_count; ++a) {
       const wire::Argument& arg = plan_.arguments[launch.first_argument + a];
       switch (arg.kind) {
         case wire::kTensor:
-          slots_[a] = reinterpret_cast<std::uintptr_t>(bound_[arg.index - profile_->first_tensor]);
+          slots_[a] = reinterpret_cast<std::uintptr_t>(bound_[arg.index - active_->profile->first_tensor]);
           break;
         case wire::kArenaOffset: slots_[a] = arena_ + arg.offset; break;
         case wire::kWeightsOffset: slots_[a] = weights_ + arg.offset; break;
@@ -304,10 +355,16 @@ Status Session::Issue(CUstream stream) {
       params_[a] = &slots_[a];
     }
     CUresult r;
-    if ((flags_ & kProgrammaticLaunch) != 0 && l != 0) {
+    const bool cooperative = active_->cooperative[l] && (flags_ & kNoCooperativeLaunch) == 0;
+    if (cooperative || ((flags_ & kProgrammaticLaunch) != 0 && l != 0)) {
       CUlaunchAttribute attr{};
-      attr.id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
-      attr.value.programmaticStreamSerializationAllowed = 1;
+      if (cooperative) {   // ordinary stream order in front of it: it starts when its predecessor has finished
+        attr.id = CU_LAUNCH_ATTRIBUTE_COOPERATIVE;
+        attr.value.cooperative = 1;
+      } else {
+        attr.id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+        attr.value.programmaticStreamSerializationAllowed = 1;
+      }
       CUlaunchConfig cfg{};
       cfg.gridDimX = launch.grid[0]; cfg.gridDimY = launch.grid[1]; cfg.gridDimZ = launch.grid[2];
       cfg.blockDimX = launch.block[0]; cfg.blockDimY = launch.block[1]; cfg.blockDimZ = launch.block[2];
@@ -315,9 +372,9 @@ Status Session::Issue(CUstream stream) {
       cfg.hStream = stream;
       cfg.attrs = &attr;
       cfg.numAttrs = 1;
-      r = cu_->cuLaunchKernelEx(&cfg, functions_[l], params_.data(), nullptr);
+      r = cu_->cuLaunchKernelEx(&cfg, active_->functions[l], params_.data(), nullptr);
     } else {
-      r = cu_->cuLaunchKernel(functions_[l], launch.grid[0], launch.grid[1], launch.grid[2], launch.block[0],
+      r = cu_->cuLaunchKernel(active_->functions[l], launch.grid[0], launch.grid[1], launch.grid[2], launch.block[0],
                               launch.block[1], launch.block[2], launch.shared_bytes, stream, params_.data(), nullptr);
     }
     ++stats_.kernel_launches;
@@ -327,13 +384,14 @@ Status Session::Issue(CUstream stream) {
 }
 
 Status Session::Replay(CUstream stream) {
-  const bool graph_safe = (profile_->flags & 1u) != 0 && (flags_ & kNoGraphReplay) == 0 && stream != nullptr;
+  const bool graph_safe = (active_->profile->flags & 1u) != 0 && (flags_ & kNoGraphReplay) == 0 && stream != nullptr;
   if (!graph_safe) return Issue(stream);
   CUstreamCaptureStatus capturing = CU_STREAM_CAPTURE_STATUS_NONE;
   if (cu_->cuStreamIsCapturing(stream, &capturing) != CUDA_SUCCESS || capturing != CU_STREAM_CAPTURE_STATUS_NONE)
     return Issue(stream);  // the caller is building its own graph: contribute plain launches
 
   CachedGraph* hit = nullptr;
+  std::vector<CachedGraph>& graphs_ = active_->graphs;
   for (CachedGraph& g : graphs_)
     if (g.key == bound_) hit = &g;
   if (hit == nullptr) {
@@ -366,16 +424,36 @@ Status Session::Replay(CUstream stream) {
 }
 
 Status Session::Enqueue(const TensorArg* inputs, std::size_t input_count, const TensorArg* outputs,
-                        std::size_t output_count, CUstream stream) {
+                        std::size_t output_count, CUstream stream, const RunSelect& select) {
+  AGI_RETURN_IF_ERROR(Select(select.denoising_steps));
+  const wire::Profile* profile = active_->profile;
+  std::vector<TensorArg> replaced;
+  if (select.noise_override != nullptr) {
+    // The override stands in for the input named "noise", whether or not the caller also passed one.
+    bool has_noise = false;
+    for (std::uint32_t i = 0; i < profile->tensor_count; ++i) {
+      const wire::Tensor& t = plan_.tensors[profile->first_tensor + i];
+      has_noise = has_noise || (t.io_kind == wire::kInput && plan_.Text(t.name) == "noise");
+    }
+    if (!has_noise) return Status(kInvalidArgument, "initial_noise_override: the selected profile has no input named noise");
+    for (std::size_t i = 0; i < input_count; ++i)
+      if (inputs[i].name == nullptr || std::string(inputs[i].name) != "noise") replaced.push_back(inputs[i]);
+    TensorArg noise = *select.noise_override;
+    noise.name = "noise";
+    replaced.push_back(noise);
+    inputs = replaced.data();
+    input_count = replaced.size();
+  }
   std::fill(bound_.begin(), bound_.end(), nullptr);
   std::size_t want_inputs = 0;
-  for (std::uint32_t i = 0; i < profile_->tensor_count; ++i)
-    want_inputs += plan_.tensors[profile_->first_tensor + i].io_kind == wire::kInput;
-  if (input_count != want_inputs || output_count != profile_->tensor_count - want_inputs)
+  for (std::uint32_t i = 0; i < profile->tensor_count; ++i)
+    want_inputs += plan_.tensors[profile->first_tensor + i].io_kind == wire::kInput;
+  if (input_count != want_inputs || output_count != profile->tensor_count - want_inputs)
     return Status(kInvalidArgument, "input or output tensor count does not match the selected profile");
   AGI_RETURN_IF_ERROR(Bind(inputs, input_count, wire::kInput));
   AGI_RETURN_IF_ERROR(Bind(outputs, output_count, wire::kOutput));
   AGI_RETURN_IF_ERROR(Prepare());
+  AGI_RETURN_IF_ERROR(Resolve());
   ++stats_.enqueues;
   return Replay(stream);
 }

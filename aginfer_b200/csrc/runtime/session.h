@@ -10,7 +10,10 @@
 //     caller's stream at the first Enqueue for a given set of tensor addresses and replayed
 //     with one graph launch afterwards (unless the caller is itself capturing, or passed the
 //     legacy null stream, in which case launches are issued one by one as in the reference);
-//   * the device is the current context's when there is one, else ordinal 0.
+//   * the device is the current context's when there is one, else ordinal 0;
+//   * kernels whose name starts with "agi_coop_" keep one CTA per SM resident and meet at grid-wide
+//     counters: they are launched with the cooperative attribute, so that the driver refuses a grid that
+//     cannot be resident at once instead of letting it wait for itself.
 #pragma once
 
 #include "cuda_api.h"
@@ -40,6 +43,7 @@ enum SessionFlags : std::uint32_t {
   kNoGraphReplay = 1u << 0,      // always issue launches one by one
   kProgrammaticLaunch = 1u << 1, // launch every kernel but the first with programmatic stream serialization
   kBlockingUpload = 1u << 2,     // upload weights with one blocking copy from the mapping, as the reference does
+  kNoCooperativeLaunch = 1u << 3, // launch agi_coop_* kernels like any other (no co-residency guarantee from the driver)
 };
 
 // Public numbering of include/aginfer/runtime.h:61-62 in the reference.
@@ -55,6 +59,14 @@ struct TensorArg {
   const std::int64_t* stride = nullptr;
   void* data = nullptr;
   std::uint64_t byte_size = 0;
+};
+
+// What of the reference's RunOptions (include/aginfer/runtime.h:84-90) selects work: the number of denoising
+// steps picks a sibling profile "<profile>/steps=<n>" of the session's profile (0 = the session's profile as
+// packaged), and a noise override stands in for the input tensor named "noise".
+struct RunSelect {
+  std::uint32_t denoising_steps = 0;
+  const TensorArg* noise_override = nullptr;
 };
 
 struct SessionStats {
@@ -77,11 +89,13 @@ class Session {
   std::uint32_t arch() const { return variant_->arch; }
   const PlanView& plan() const { return plan_; }
   const wire::Profile& profile() const { return *profile_; }
+  // The profile the last Enqueue ran (the session's own, or a step-count sibling of it).
+  const wire::Profile& active_profile() const { return *active_->profile; }
   const SessionStats& stats() const { return stats_; }
   bool HasProfile(const std::string& name) const { return plan_.Find(name) != nullptr; }
 
   Status Enqueue(const TensorArg* inputs, std::size_t input_count, const TensorArg* outputs,
-                 std::size_t output_count, CUstream stream);
+                 std::size_t output_count, CUstream stream, const RunSelect& select = RunSelect());
 
  private:
   Session() = default;
@@ -90,6 +104,8 @@ class Session {
   Status Upload(const std::uint8_t* src, std::uint64_t bytes);
   Status Issue(CUstream stream);          // the launch loop
   Status Replay(CUstream stream);         // graph path; falls back to Issue
+  Status Select(std::uint32_t denoising_steps);   // points active_ at the profile to run
+  Status Resolve();                       // functions and attributes of the active profile, once per profile
 
   const Package* package_ = nullptr;
   const wire::VariantEntry* variant_ = nullptr;
@@ -104,7 +120,6 @@ class Session {
   bool retained_primary_ = false;
   CUmodule module_ = nullptr;
   CUdeviceptr weights_ = 0, arena_ = 0, workspace_ = 0;
-  std::vector<CUfunction> functions_;     // one per launch of the profile
   std::vector<void*> bound_;              // device address per profile tensor
   std::vector<std::uint64_t> slots_;
   std::vector<void*> params_;
@@ -114,7 +129,16 @@ class Session {
     CUgraphExec exec = nullptr;
     std::uint64_t last_use = 0;
   };
-  std::vector<CachedGraph> graphs_;
+  // Per profile the session has run: the session's own first, step-count siblings as they are asked for.
+  struct ProfileState {
+    const wire::Profile* profile = nullptr;
+    bool resolved = false;
+    std::vector<CUfunction> functions;    // one per launch of the profile
+    std::vector<bool> cooperative;        // per launch: kernel name starts with "agi_coop_"
+    std::vector<CachedGraph> graphs;
+  };
+  std::vector<std::unique_ptr<ProfileState>> states_;
+  ProfileState* active_ = nullptr;
   SessionStats stats_;
 };
 

@@ -234,6 +234,38 @@ def stream_tiling(M: int, N: int, K: int, elem: int, extra_rows: int = 0, contig
             "shared_bytes": slots * held * row_bytes(chunk_windows) + tail}
 
 
+# ---- persistent block kernel (csrc/kernels/dit_block.cuh) ------------------------------------------------
+DIT_TABLE_ORDER = ("to_q.weight", "to_q.bias", "to_k.weight", "to_k.bias", "to_v.weight", "to_v.bias", "to_out.weight",
+                   "to_out.bias", "fc1.weight", "fc1.bias", "fc2.weight", "fc2.bias", "adaln", "context_k", "context_v")
+DIT_SLOT_BYTES = 16 * (16 * 64 + 64)     # a ring slot: 16 weight rows x (1 KB + 64 bytes of padding)
+DIT_HEADER_BYTES = 256
+DIT_MAX_SPAN = 1536                      # K elements a consumer warp keeps as MMA B fragments
+MAX_DYNAMIC_SHARED = 227 * 1024
+
+
+def dit_block_span(mlp: int) -> int | None:
+    """K span of the MLP down projection: the largest divisor of ``mlp`` that is a multiple of 32 and at most 1536."""
+    return next((s for s in range(min(mlp, DIT_MAX_SPAN) // 32 * 32, 0, -32) if mlp % s == 0), None)
+
+
+def dit_block_geometry(T: int, D: int, heads: int, head_dim: int, mlp: int, ctx: int, layers: int) -> dict[str, int] | None:
+    """Shared-memory plan of the persistent block kernel, or None when the shape is outside its limits
+    (mirrors ``ditb::phase_region_bytes``)."""
+    span = dit_block_span(mlp)
+    if (span is None or not 1 <= T <= 24 or D % 32 or D > DIT_MAX_SPAN or mlp % 16 or head_dim % 16 or head_dim > 64
+            or heads * head_dim != D or not 1 <= layers <= 32 or ctx < 1):
+        return None
+    pitch = max(D, span) * 2 + 64
+    gemm_bytes = T * pitch + 8 * 16 * (T | 1) * 4
+    keys = ceil_div(max(ctx, T), 16) * 16
+    attn_bytes = max(2 * keys * (head_dim + 8) * 2, 8 * 16 * (head_dim + 2) * 4)
+    region = ceil_div(max(gemm_bytes, attn_bytes), 128) * 128
+    slots = min(12, (MAX_DYNAMIC_SHARED - DIT_HEADER_BYTES - region) // DIT_SLOT_BYTES)
+    if slots < 3:
+        return None
+    return {"slots": slots, "region": region, "shared_bytes": DIT_HEADER_BYTES + region + slots * DIT_SLOT_BYTES}
+
+
 def grid_for(work_items: int, threads: int = 256, cap: int = SM_COUNT * 8) -> int:
     return max(1, min(cap, ceil_div(work_items, threads)))
 
@@ -266,6 +298,7 @@ class RecipeBuilder:
         # Split-K scratch of the tensor-core GEMMs lives outside the stack discipline of alloc/release:
         # its arrival counters must stay zero between launches for the whole life of the session.
         self._tc_scratch = (self.alloc(TC_SCRATCH_BYTES), self.alloc(TC_COUNTER_BYTES))
+        self._dit_scratch: dict[tuple[int, int, int], tuple[Arena, Arena]] = {}
 
     # ---- address spaces -------------------------------------------------------------------
     def alloc(self, nbytes: int, align: int = ALIGN) -> Arena:
@@ -694,6 +727,44 @@ class RecipeBuilder:
                      U32(t["chunk_windows"]), F32((ln or {}).get("eps", 0.0))],
                     shared_bytes=t["shared_bytes"], op="fused_linear_bf16",
                     algorithm=f"bulk_stream_r{rows}_t{tiles}_x{len(parts)}" + ("_ln" if ln else ""))
+
+    # ---- persistent block kernel ----------------------------------------------------------
+    def store_pointers(self, table: Arena, first: int, pointers: Sequence[Pointer]) -> None:
+        """Write device addresses into consecutive 8-byte slots of an arena table, 16 per launch: how a
+        persistent kernel receives more pointers than a parameter list should carry."""
+        dummy = Arena(0)
+        for i in range(0, len(pointers), 16):
+            batch = list(pointers[i:i + 16])
+            self.launch("agi_store_pointers16", (1, 1, 1), (32, 1, 1),
+                        [table, U32(first + i), U32(len(batch)), *batch, *([dummy] * (16 - len(batch)))],
+                        op="pointer_table", algorithm="store16")
+
+    def dit_blocks(self, table: Arena, seq: Pointer, qkv: Pointer, attn: Pointer, ff: Pointer, *, layers: int, T: int,
+                   D: int, heads: int, head_dim: int, mlp: int, ctx: int, cross_mask: int, mod_offset: int,
+                   eps: float, scale: float | None = None) -> None:
+        """A stack of DiT blocks as ONE launch of the persistent block kernel (``agi_coop_dit_blocks_bf16_t*``):
+        one CTA per SM walks every block; the weight stream runs ahead of the compute through a shared-memory
+        ring and never stops at a phase boundary.  ``table``: 16 pointers per block (``DIT_TABLE_ORDER``),
+        written earlier in the profile with ``store_pointers``.  ``mod_offset``: elements from a block's AdaLN
+        pointer to this step's (scale | shift) row.  ``seq`` [T, D] is updated in place."""
+        span = dit_block_span(mlp)
+        geometry = dit_block_geometry(T, D, heads, head_dim, mlp, ctx, layers)
+        if geometry is None or span is None:
+            raise ValueError("shape is outside what the persistent block kernel covers")
+        scratch = self._dit_scratch.get((T, D, mlp))
+        if scratch is None:
+            # K-span partial sums of the MLP down projection, and the arrival counters of its feature groups
+            # (zero between launches for the life of the session, like the split-K counters above)
+            scratch = (self.alloc((mlp // span) * T * D * 4), self.alloc(D // 16 * 4))
+            self._dit_scratch[(T, D, mlp)] = scratch
+        partial, group_counters = scratch
+        tiles = 2 if T <= 16 else 3
+        self.launch(f"agi_coop_dit_blocks_bf16_t{tiles}", (SM_COUNT, 1, 1), (288, 1, 1),
+                    [table, seq, qkv, attn, ff, partial, group_counters, self.counter(), Arena(STATUS_WORD), U32(layers),
+                     U32(T), U32(D), U32(heads), U32(head_dim), U32(mlp), U32(span), U32(ctx), U32(cross_mask),
+                     U32(mod_offset), U32(geometry["slots"]), F32(eps), F32(scale if scale is not None else head_dim ** -0.5)],
+                    shared_bytes=geometry["shared_bytes"], op="dit_blocks",
+                    algorithm=f"persistent_ring{geometry['slots']}_span{span}_x{layers}")
 
     # ---- outputs --------------------------------------------------------------------------
     def plan(self) -> dict[str, Any]:

@@ -23,7 +23,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Mapping
 
-from .builder import Arena, F32, RecipeBuilder, Tensor, U32, Weight, io, grid_for
+from .builder import Arena, F32, RecipeBuilder, Tensor, U32, Weight, dit_block_geometry, io, grid_for
 
 
 @dataclass(frozen=True)
@@ -113,13 +113,20 @@ def synthetic_inputs(cfg: DitConfig, seed: int = 2) -> dict:
 
 def build_recipe(cfg: DitConfig = DitConfig(), weights: Mapping[str, tuple[str, tuple[int, ...]]] | None = None,
                  gemm_tactic: str = "auto", profile: str = "default", stream_profile: bool = False,
-                 fuse: bool = True, batch_kv: bool = True) -> RecipeBuilder:
+                 fuse: bool = True, batch_kv: bool = True, block_kernel: bool | None = None) -> RecipeBuilder:
+    """``block_kernel``: run each denoising step's blocks as one launch of the persistent block kernel
+    (default: whenever the shape fits it and the GEMM tactic is left to the builder)."""
     D, T, H, S = cfg.hidden, cfg.tokens, cfg.horizon, cfg.steps
+    fits = dit_block_geometry(T, D, cfg.heads, cfg.head_dim, cfg.mlp, cfg.backbone_tokens, cfg.layers) is not None
+    if block_kernel is None:
+        block_kernel = fits and gemm_tactic == "auto"
+    if block_kernel and not fits:
+        raise ValueError("this shape is outside what the persistent block kernel covers")
     r = RecipeBuilder(weights or {k: ("BF16", v) for k, v in weight_shapes(cfg).items()})
     r.begin_profile(profile, [io("backbone_features", "BF16", [cfg.backbone_tokens, cfg.backbone_dim]),
                               io("state", "BF16", [1, cfg.state_dim]),
                               io("noise", "BF16", [H, cfg.action_dim])],
-                    [io("actions", "F32", [H, cfg.action_dim])])
+                    [io("actions", "F32", [H, cfg.action_dim]), io("status", "I32", [1])])
     BF = 2
 
     def lin(x, name, y, M, N, K, **kw):
@@ -192,6 +199,17 @@ def build_recipe(cfg: DitConfig = DitConfig(), weights: Mapping[str, tuple[str, 
     dec_hid = r.alloc(H * cfg.encoder_hidden * BF)
     velocity = r.alloc(H * cfg.action_dim * BF)
 
+    if block_kernel:
+        # the blocks' pointers, once per chunk: 16 slots per block in the order the kernel reads them
+        table = r.alloc(cfg.layers * 16 * 8)
+        for l in range(cfg.layers):
+            b = f"{P}.dit.blocks.{l}"
+            names = ["attn.to_q", "attn.to_k", "attn.to_v", "attn.to_out", "ff.fc1", "ff.fc2"]
+            row = [Weight(f"{b}.{n}.{kind}") for n in names for kind in ("weight", "bias")]
+            row += [mods[l], *(kv[l] if cfg.is_cross(l) else (mods[l], mods[l]))]
+            r.store_pointers(table, l * 16, row)
+        cross_mask = sum(1 << l for l in range(cfg.layers) if cfg.is_cross(l))
+
     for step in range(S):
         mod_row = step * 2 * D * BF       # this step's (scale | shift) row inside each mods[l]
         # action encoder: tokens 1..H of the sequence
@@ -204,7 +222,11 @@ def build_recipe(cfg: DitConfig = DitConfig(), weights: Mapping[str, tuple[str, 
                                           U32(H)], H * D, "add_position_embedding")
         elementwise("agi_copy_rows_bf16", [state_tok, seq, U32(1), U32(D), U32(D), U32(D)], D, "copy")
 
-        for l in range(cfg.layers):
+        if block_kernel:
+            r.dit_blocks(table, seq, qkv, attn, ff, layers=cfg.layers, T=T, D=D, heads=cfg.heads, head_dim=cfg.head_dim,
+                         mlp=cfg.mlp, ctx=cfg.backbone_tokens, cross_mask=cross_mask, mod_offset=step * 2 * D,
+                         eps=cfg.ln_eps)
+        for l in range(0 if block_kernel else cfg.layers):
             b = f"{P}.dit.blocks.{l}"
             adaln = {"eps": cfg.ln_eps, "scale": mods[l] + mod_row, "shift": mods[l] + (mod_row + D * BF)}
             part = lambda name, n: (Weight(f"{b}.{name}.weight"), Weight(f"{b}.{name}.bias"), n)
@@ -232,6 +254,7 @@ def build_recipe(cfg: DitConfig = DitConfig(), weights: Mapping[str, tuple[str, 
 
     r.launch("agi_copy_u32", (1, 1, 1), (256, 1, 1), [x_f32, Tensor("actions"), U32(H * cfg.action_dim)],
              op="copy_out")
+    r.export_status(Tensor("status"))   # 0 = every bounded wait of the chunk was satisfied
 
     if stream_profile:
         # Measurement profile: the tensor-core GEMM launches of ONE denoising step, back to back and

@@ -21,7 +21,7 @@ STATUS_NAMES = ("OK", "INVALID_ARGUMENT", "NOT_FOUND", "IO_ERROR", "CORRUPT_PACK
 DTYPES = {"F32": 0, "F16": 1, "BF16": 2, "F8_E4M3": 3, "I32": 4}
 DTYPE_NAMES = {v: k for k, v in DTYPES.items()}
 HOST, DEVICE = 0, 1
-NO_GRAPH_REPLAY, PROGRAMMATIC_LAUNCH, BLOCKING_UPLOAD = 1, 2, 4
+NO_GRAPH_REPLAY, PROGRAMMATIC_LAUNCH, BLOCKING_UPLOAD, NO_COOPERATIVE_LAUNCH = 1, 2, 4, 8
 MAX_RANK = 8
 
 

@@ -83,8 +83,16 @@ typedef struct agi_tensor_info {
   uint64_t byte_size;
 } agi_tensor_info;
 
-/* runtime.h:84-90 RunOptions.  Accepted and ignored, as in the reference (runtime.cc:499-500):
- * a recipe's step count and noise are fixed by its plan and its input tensors. */
+/* runtime.h:84-90 RunOptions.  The reference accepts and ignores them (runtime.cc:499-500); here the two
+ * that can select work in a static plan do:
+ *   denoising_steps: 0 runs the session's profile as packaged; n > 0 runs its sibling profile
+ *     "<profile>/steps=<n>" (a recipe unrolled for n Euler steps, same tensors), AGI_INVALID_ARGUMENT when
+ *     the package carries none for n;
+ *   initial_noise_override: when not NULL, stands in for the input tensor named "noise" (its own `name`
+ *     is not looked at; validated against the profile like any other view; AGI_INVALID_ARGUMENT when the
+ *     profile has no such input).  The caller may then leave "noise" out of `inputs`.
+ * seed, deterministic and math_mode stay without effect: noise is an explicit input, every kernel of the
+ * bundle is deterministic, and the arithmetic of a recipe is fixed when it is packaged. */
 typedef struct agi_run_options {
   uint32_t denoising_steps;
   uint32_t deterministic;
@@ -98,6 +106,7 @@ typedef struct agi_run_options {
 #define AGI_SESSION_NO_GRAPH_REPLAY   (1u << 0) /* issue every launch with cuLaunchKernel, as the reference does */
 #define AGI_SESSION_PROGRAMMATIC_LAUNCH (1u << 1) /* programmatic stream serialization between consecutive launches */
 #define AGI_SESSION_BLOCKING_UPLOAD   (1u << 2) /* one blocking cuMemcpyHtoD of the weights, as the reference does */
+#define AGI_SESSION_NO_COOPERATIVE_LAUNCH (1u << 3) /* launch agi_coop_* kernels without the cooperative attribute */
 
 typedef struct agi_runtime agi_runtime;
 typedef struct agi_model agi_model;
@@ -153,7 +162,7 @@ typedef struct agi_session_stats {
   uint64_t kernel_launches;   /* cuLaunchKernel calls issued, including those recorded into a graph */
   uint64_t graph_launches;    /* Enqueue calls served by replaying a captured graph */
   uint64_t graphs_built;
-  uint64_t launches_per_enqueue; /* launch records in the selected profile */
+  uint64_t launches_per_enqueue; /* launch records in the profile the last Enqueue ran */
   double upload_seconds;      /* wall time of the one-time weight upload */
 } agi_session_stats;
 AGI_API agi_status agi_session_get_stats(const agi_session* session, agi_session_stats* out);

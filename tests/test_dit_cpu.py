@@ -20,21 +20,47 @@ def test_weight_inventory_matches_the_published_size():
     assert acc["once"] + acc["per_step"] == acc["total_weights"]
 
 
-def test_recipe_compiles_and_is_one_graph_safe_profile():
-    cfg = dit.DitConfig()
-    r = dit.build_recipe(cfg)
+def _check_recipe(cfg, r, expect_kernels):
     plan = r.plan()
     compiled = planfmt.compile_execution_plan(plan, CudaArch.SM100, weight_size=r.weight_bytes)
-    assert compiled.input_names == ("backbone_features", "state", "noise") and compiled.output_names == ("actions",)
+    assert compiled.input_names == ("backbone_features", "state", "noise") and compiled.output_names == ("actions", "status")
     launches = plan["shape_dispatch"][0]["launches"]
     assert plan["cuda_graph_templates"] == [{"profile": "default"}]
     per_step = [l for l in launches if l["kernel"] == "agi_euler_step"]
     assert len(per_step) == cfg.steps
     kernels = {l["kernel"] for l in launches}
-    assert {"agi_gemm_tc_bf16_x16", "agi_gemm_stream_bf16_t3", "agi_attention_mma_bf16", "agi_layernorm_bf16"} <= kernels
+    assert expect_kernels <= kernels
     # every weight of the checkpoint is used by some launch
     used = {a["weights_offset"] for l in launches for a in l["arguments"] if "weights_offset" in a}
     assert used == set(r.weight_offsets.values())
+    return launches
+
+
+def test_recipe_compiles_and_is_one_graph_safe_profile():
+    cfg = dit.DitConfig()
+    launches = _check_recipe(cfg, dit.build_recipe(cfg, block_kernel=False),
+                             {"agi_gemm_tc_bf16_x16", "agi_gemm_stream_bf16_t3", "agi_attention_mma_bf16", "agi_layernorm_bf16"})
+    assert len(launches) > 400
+
+
+def test_block_kernel_recipe_is_one_launch_per_denoising_step():
+    cfg = dit.DitConfig()
+    launches = _check_recipe(cfg, dit.build_recipe(cfg), {"agi_coop_dit_blocks_bf16_t3", "agi_store_pointers16"})
+    blocks = [l for l in launches if l["kernel"].startswith("agi_coop_dit_blocks")]
+    assert len(blocks) == cfg.steps and len(launches) <= 150
+    for step, l in enumerate(blocks):
+        assert l["grid"] == [148, 1, 1] and l["block"] == [288, 1, 1] and l["shared_bytes"] <= 227 * 1024
+        scalars = [a["scalar_u32"] for a in l["arguments"] if "scalar_u32" in a]
+        layers, T, D, heads, head_dim, mlp, span, ctx, cross_mask, mod_offset, slots = scalars
+        assert (layers, T, D, heads, head_dim, mlp, ctx) == (16, 17, 1536, 32, 48, 6144, 300)
+        assert span == 1536 and cross_mask == 0x5555 and mod_offset == step * 2 * D and slots >= 3
+    # each launch gets its own grid-wide arrival counter, inside the per-run area the prologue clears
+    counters = [l["arguments"][7]["arena_offset"] for l in blocks]
+    assert len(set(counters)) == cfg.steps and all(64 <= c < 1024 for c in counters)
+    # the tiny shape is covered too; a shape outside the kernel's limits falls back to separate launches
+    assert any(l["kernel"].startswith("agi_coop_dit_blocks") for l in dit.build_recipe(TINY).plan()["shape_dispatch"][0]["launches"])
+    wide = dit.DitConfig(layers=2, hidden=2048, heads=32, head_dim=64, mlp=4096)
+    assert not any(l["kernel"].startswith("agi_coop") for l in dit.build_recipe(wide).plan()["shape_dispatch"][0]["launches"])
 
 
 def test_oracle_runs_and_is_deterministic_on_a_tiny_shape():

@@ -4,6 +4,7 @@ from __future__ import annotations
 import pytest
 import torch
 
+from aginfer_b200 import runtime as rt
 from aginfer_b200.recipes import dit
 from aginfer_b200.recipes.package import build_aim
 from aginfer_b200.runner import Runner
@@ -14,37 +15,49 @@ from tests.test_dit_cpu import TINY
 pytestmark = pytest.mark.gpu
 
 
-def run_chunk(tmp_path, cfg, weights, inputs, gemm_tactic="auto", repeats=2):
-    recipe = dit.build_recipe(cfg, gemm_tactic=gemm_tactic)
+def run_chunk(tmp_path, cfg, weights, inputs, gemm_tactic="auto", repeats=2, block_kernel=None, flags=0):
+    recipe = dit.build_recipe(cfg, gemm_tactic=gemm_tactic, block_kernel=block_kernel)
     aim = build_aim(tmp_path, weights, recipe, steps=cfg.steps, action_horizon=cfg.horizon, state_length=cfg.state_dim)
-    runner = Runner(aim)
+    runner = Runner(aim, flags=flags)
     dev = {k: v.cuda() for k, v in inputs.items()}
     out = runner.empty_outputs()
     for _ in range(repeats):
         runner.run(dev, out)
     torch.cuda.synchronize()
+    assert int(out["status"].item()) == 0, f"a bounded wait ran out: status {int(out['status'].item()):#x}"
     return out["actions"].cpu(), runner.stats()
 
 
-@pytest.mark.parametrize("tactic", ["simt", "auto"])
-def test_tiny_dit_matches_oracle(tmp_path, tactic):
+@pytest.mark.parametrize("tactic,block_kernel", [("simt", False), ("auto", False), ("auto", True)])
+def test_tiny_dit_matches_oracle(tmp_path, tactic, block_kernel):
     w, x = dit.synthetic_weights(TINY), dit.synthetic_inputs(TINY)
-    got, stats = run_chunk(tmp_path, TINY, w, x, tactic)
+    got, stats = run_chunk(tmp_path, TINY, w, x, tactic, block_kernel=block_kernel)
     want = oracle_dit.forward(TINY, w, x["backbone_features"], x["state"], x["noise"])
     assert ops.cosine(got, want) >= 0.999
     assert ops.max_rel_err(got, want) < 2e-2
     assert stats["graph_launches"] == 2 and stats["graphs_built"] == 1
 
 
-def test_full_size_action_chunk_matches_oracle(tmp_path):
+@pytest.mark.parametrize("flags", [rt.NO_GRAPH_REPLAY, rt.NO_GRAPH_REPLAY | rt.NO_COOPERATIVE_LAUNCH, rt.PROGRAMMATIC_LAUNCH])
+def test_tiny_dit_block_kernel_launch_modes(tmp_path, flags):
+    # plain launches with and without the cooperative attribute, and graph replay with programmatic edges
+    w, x = dit.synthetic_weights(TINY), dit.synthetic_inputs(TINY)
+    got, _ = run_chunk(tmp_path, TINY, w, x, block_kernel=True, flags=flags)
+    base, _ = run_chunk(tmp_path / "base", TINY, w, x, block_kernel=True)
+    assert torch.equal(got, base)
+
+
+@pytest.mark.parametrize("block_kernel", [False, True])
+def test_full_size_action_chunk_matches_oracle(tmp_path, block_kernel):
     # BASELINE config 3: 16 blocks x 1536, 17 tokens, 300 backbone tokens, 4 Euler steps, seed 2
     cfg = dit.DitConfig()
     w, x = dit.synthetic_weights(cfg, seed=2), dit.synthetic_inputs(cfg, seed=2)
-    got, stats = run_chunk(tmp_path, cfg, w, x)
+    got, stats = run_chunk(tmp_path, cfg, w, x, block_kernel=block_kernel)
     want = oracle_dit.forward(cfg, w, x["backbone_features"], x["state"], x["noise"])
     cos, err = ops.cosine(got, want), ops.max_rel_err(got, want)
-    print(f"full DiT: cosine={cos:.6f} max_rel_err={err:.3e} launches/chunk={stats['launches_per_enqueue']}")
+    print(f"full DiT (block kernel {block_kernel}): cosine={cos:.6f} max_rel_err={err:.3e} "
+          f"launches/chunk={stats['launches_per_enqueue']}")
     assert cos >= 0.999 and err < 2e-2
-    # a fresh session reproduces the chunk bit for bit: split-K partials are summed in slice order
-    again, _ = run_chunk(tmp_path / "again", cfg, w, x, repeats=1)
+    # a fresh session reproduces the chunk bit for bit: partial sums are added in a fixed order
+    again, _ = run_chunk(tmp_path / "again", cfg, w, x, repeats=1, block_kernel=block_kernel)
     assert torch.equal(again, got)
