@@ -250,16 +250,17 @@ def dit_block_span(mlp: int) -> int | None:
 
 def dit_block_geometry(T: int, D: int, heads: int, head_dim: int, mlp: int, ctx: int, layers: int) -> dict[str, int] | None:
     """Shared-memory plan of the persistent block kernel, or None when the shape is outside its limits
-    (mirrors ``ditb::phase_region_bytes``)."""
+    (mirrors ``ditb::exchange_bytes`` and ``ditb::attention_bytes``)."""
     span = dit_block_span(mlp)
     if (span is None or not 1 <= T <= 24 or D % 32 or D > DIT_MAX_SPAN or mlp % 16 or head_dim % 16 or head_dim > 64
             or heads * head_dim != D or not 1 <= layers <= 32 or ctx < 1):
         return None
-    pitch = max(D, span) * 2 + 64
-    gemm_bytes = T * pitch + 8 * 16 * (T | 1) * 4
+    # then the attention tile (keys and values of a head)
+    # the table's copy, the consumers' exchange area (partial tiles, row statistics), AdaLN scale | shift
+    exchange = 32 * 16 * 8 + ceil_div(8 * 16 * (T | 1) * 4 + 2 * 8 * 24 * 4 + 64, 128) * 128 + 4 * DIT_MAX_SPAN
     keys = ceil_div(max(ctx, T), 16) * 16
-    attn_bytes = max(2 * keys * (head_dim + 8) * 2, 8 * 16 * (head_dim + 2) * 4)
-    region = ceil_div(max(gemm_bytes, attn_bytes), 128) * 128
+    attention = ceil_div(max(2 * keys * (head_dim + 8) * 2, 8 * 16 * (head_dim + 2) * 4), 128) * 128
+    region = exchange + attention
     slots = min(12, (MAX_DYNAMIC_SHARED - DIT_HEADER_BYTES - region) // DIT_SLOT_BYTES)
     if slots < 3:
         return None
@@ -331,6 +332,7 @@ class RecipeBuilder:
                       graph_safe: bool = True) -> None:
         self._profile = Profile(name, [dict(i) for i in inputs], [dict(o) for o in outputs], [], graph_safe)
         self.profiles.append(self._profile)
+        self._counter_cursor = 64          # every profile clears the counter area itself, so slots are per profile
         # prologue: clear status word and counters
         self.launch("agi_fill_u32", (1, 1, 1), (256, 1, 1), [Arena(0), U32(0), U32(self.reserved // 4)],
                     op="prologue", algorithm="fill_u32")
@@ -739,6 +741,18 @@ class RecipeBuilder:
                         [table, U32(first + i), U32(len(batch)), *batch, *([dummy] * (16 - len(batch)))],
                         op="pointer_table", algorithm="store16")
 
+    def dit_scratch(self, T: int, D: int, mlp: int) -> tuple[Arena, Arena]:
+        """Scratch of the persistent block kernel: K-span partial sums of the MLP down projection and the arrival
+        counters of its feature groups (zero between launches for the life of the session, like the split-K
+        counters).  Outside the stack discipline of alloc/release: call it before the first ``mark`` of a recipe
+        that releases arena space between profiles."""
+        scratch = self._dit_scratch.get((T, D, mlp))
+        if scratch is None:
+            span = dit_block_span(mlp)
+            scratch = (self.alloc((mlp // span) * T * D * 4), self.alloc(D // 16 * 4))
+            self._dit_scratch[(T, D, mlp)] = scratch
+        return scratch
+
     def dit_blocks(self, table: Arena, seq: Pointer, qkv: Pointer, attn: Pointer, ff: Pointer, *, layers: int, T: int,
                    D: int, heads: int, head_dim: int, mlp: int, ctx: int, cross_mask: int, mod_offset: int,
                    eps: float, scale: float | None = None) -> None:
@@ -751,15 +765,9 @@ class RecipeBuilder:
         geometry = dit_block_geometry(T, D, heads, head_dim, mlp, ctx, layers)
         if geometry is None or span is None:
             raise ValueError("shape is outside what the persistent block kernel covers")
-        scratch = self._dit_scratch.get((T, D, mlp))
-        if scratch is None:
-            # K-span partial sums of the MLP down projection, and the arrival counters of its feature groups
-            # (zero between launches for the life of the session, like the split-K counters above)
-            scratch = (self.alloc((mlp // span) * T * D * 4), self.alloc(D // 16 * 4))
-            self._dit_scratch[(T, D, mlp)] = scratch
-        partial, group_counters = scratch
+        partial, group_counters = self.dit_scratch(T, D, mlp)
         tiles = 2 if T <= 16 else 3
-        self.launch(f"agi_coop_dit_blocks_bf16_t{tiles}", (SM_COUNT, 1, 1), (288, 1, 1),
+        self.launch(f"agi_coop_dit_blocks_bf16_t{tiles}", (SM_COUNT, 1, 1), (384, 1, 1),
                     [table, seq, qkv, attn, ff, partial, group_counters, self.counter(), Arena(STATUS_WORD), U32(layers),
                      U32(T), U32(D), U32(heads), U32(head_dim), U32(mlp), U32(span), U32(ctx), U32(cross_mask),
                      U32(mod_offset), U32(geometry["slots"]), F32(eps), F32(scale if scale is not None else head_dim ** -0.5)],

@@ -20,8 +20,8 @@ Tensor names follow Hugging Face conventions (``<module>.weight`` / ``.bias``, w
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
-from typing import Mapping
+from dataclasses import dataclass, replace
+from typing import Mapping, Sequence
 
 from .builder import Arena, F32, RecipeBuilder, Tensor, U32, Weight, dit_block_geometry, io, grid_for
 
@@ -113,16 +113,36 @@ def synthetic_inputs(cfg: DitConfig, seed: int = 2) -> dict:
 
 def build_recipe(cfg: DitConfig = DitConfig(), weights: Mapping[str, tuple[str, tuple[int, ...]]] | None = None,
                  gemm_tactic: str = "auto", profile: str = "default", stream_profile: bool = False,
-                 fuse: bool = True, batch_kv: bool = True, block_kernel: bool | None = None) -> RecipeBuilder:
+                 fuse: bool = True, batch_kv: bool = True, block_kernel: bool | None = None,
+                 step_profiles: Sequence[int] = ()) -> RecipeBuilder:
     """``block_kernel``: run each denoising step's blocks as one launch of the persistent block kernel
-    (default: whenever the shape fits it and the GEMM tactic is left to the builder)."""
-    D, T, H, S = cfg.hidden, cfg.tokens, cfg.horizon, cfg.steps
+    (78 launches per chunk instead of 506).  Off by default: measured on B200 it is the slower of the two
+    (3.9 ms per chunk against 2.9 ms), see the kernel's header for where its time goes.
+    ``step_profiles``: further numbers of Euler steps to package as sibling profiles ``<profile>/steps=<n>``
+    (same tensors; the loader runs one of them when the caller's RunOptions ask for n denoising steps).
+    ``stream_profile``: also emit the measurement profiles of the dominant kernel."""
+    D, T = cfg.hidden, cfg.tokens
     fits = dit_block_geometry(T, D, cfg.heads, cfg.head_dim, cfg.mlp, cfg.backbone_tokens, cfg.layers) is not None
     if block_kernel is None:
-        block_kernel = fits and gemm_tactic == "auto"
+        block_kernel = False
     if block_kernel and not fits:
         raise ValueError("this shape is outside what the persistent block kernel covers")
     r = RecipeBuilder(weights or {k: ("BF16", v) for k, v in weight_shapes(cfg).items()})
+    if block_kernel:
+        r.dit_scratch(T, D, cfg.mlp)      # outlives every profile: allocated before the first mark
+    variants = [(profile, cfg.steps)] + [(f"{profile}/steps={n}", n) for n in step_profiles]
+    for i, (name, steps) in enumerate(variants):
+        mark = r.mark()                   # profiles never run concurrently: they share the arena above the mark
+        _emit_chunk(r, replace(cfg, steps=steps), name, gemm_tactic, fuse, batch_kv, block_kernel,
+                    measure=stream_profile and i == 0)
+        r.release(mark)
+    return r
+
+
+def _emit_chunk(r: RecipeBuilder, cfg: DitConfig, profile: str, gemm_tactic: str, fuse: bool, batch_kv: bool,
+                block_kernel: bool, measure: bool) -> None:
+    """One profile: the whole action chunk of ``cfg.steps`` Euler steps."""
+    D, T, H, S = cfg.hidden, cfg.tokens, cfg.horizon, cfg.steps
     r.begin_profile(profile, [io("backbone_features", "BF16", [cfg.backbone_tokens, cfg.backbone_dim]),
                               io("state", "BF16", [1, cfg.state_dim]),
                               io("noise", "BF16", [H, cfg.action_dim])],
@@ -256,7 +276,24 @@ def build_recipe(cfg: DitConfig = DitConfig(), weights: Mapping[str, tuple[str, 
              op="copy_out")
     r.export_status(Tensor("status"))   # 0 = every bounded wait of the chunk was satisfied
 
-    if stream_profile:
+    if measure and block_kernel:
+        # Measurement profiles of the persistent block kernel: the pointer table plus 1 resp. 5 launches of one
+        # denoising step's blocks and nothing else (same kernel, geometry and weights as above; the residual stream
+        # starts from zeros).  (time of "blocks_5" - time of "blocks_1") / 4 is the duration of one launch.
+        for count in (1, 5):
+            r.begin_profile(f"blocks_{count}", [io("token", "I32", [1])], [io("status", "I32", [1])])
+            r.launch("agi_fill_u32", (4, 1, 1), (256, 1, 1), [seq, U32(0), U32(T * D * BF // 4)], op="clear")
+            for l in range(cfg.layers):
+                b = f"{P}.dit.blocks.{l}"
+                names = ["attn.to_q", "attn.to_k", "attn.to_v", "attn.to_out", "ff.fc1", "ff.fc2"]
+                row = [Weight(f"{b}.{n}.{kind}") for n in names for kind in ("weight", "bias")]
+                r.store_pointers(table, l * 16, row + [mods[l], *(kv[l] if cfg.is_cross(l) else (mods[l], mods[l]))])
+            for _ in range(count):
+                r.dit_blocks(table, seq, qkv, attn, ff, layers=cfg.layers, T=T, D=D, heads=cfg.heads,
+                             head_dim=cfg.head_dim, mlp=cfg.mlp, ctx=cfg.backbone_tokens, cross_mask=cross_mask,
+                             mod_offset=0, eps=cfg.ln_eps)
+            r.export_status(Tensor("status"))
+    elif measure:
         # Measurement profile: the tensor-core GEMM launches of ONE denoising step, back to back and
         # nothing else (same kernels, tilings and weights as above; activations are whatever the arena
         # holds).  Timing it gives the weight-streaming rate of the dominant kernel in isolation.
@@ -272,7 +309,6 @@ def build_recipe(cfg: DitConfig = DitConfig(), weights: Mapping[str, tuple[str, 
                            act="gelu_tanh", fuse=fuse)
             lin(ff, f"{b}.ff.fc2", seq, T, D, cfg.mlp, residual=seq)
         r.export_status(Tensor("status"))
-    return r
 
 
 def stream_profile_bytes(cfg: DitConfig = DitConfig()) -> tuple[int, int]:

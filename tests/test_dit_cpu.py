@@ -38,18 +38,18 @@ def _check_recipe(cfg, r, expect_kernels):
 
 def test_recipe_compiles_and_is_one_graph_safe_profile():
     cfg = dit.DitConfig()
-    launches = _check_recipe(cfg, dit.build_recipe(cfg, block_kernel=False),
+    launches = _check_recipe(cfg, dit.build_recipe(cfg),
                              {"agi_gemm_tc_bf16_x16", "agi_gemm_stream_bf16_t3", "agi_attention_mma_bf16", "agi_layernorm_bf16"})
     assert len(launches) > 400
 
 
 def test_block_kernel_recipe_is_one_launch_per_denoising_step():
     cfg = dit.DitConfig()
-    launches = _check_recipe(cfg, dit.build_recipe(cfg), {"agi_coop_dit_blocks_bf16_t3", "agi_store_pointers16"})
+    launches = _check_recipe(cfg, dit.build_recipe(cfg, block_kernel=True), {"agi_coop_dit_blocks_bf16_t3", "agi_store_pointers16"})
     blocks = [l for l in launches if l["kernel"].startswith("agi_coop_dit_blocks")]
     assert len(blocks) == cfg.steps and len(launches) <= 150
     for step, l in enumerate(blocks):
-        assert l["grid"] == [148, 1, 1] and l["block"] == [288, 1, 1] and l["shared_bytes"] <= 227 * 1024
+        assert l["grid"] == [148, 1, 1] and l["block"] == [384, 1, 1] and l["shared_bytes"] <= 227 * 1024
         scalars = [a["scalar_u32"] for a in l["arguments"] if "scalar_u32" in a]
         layers, T, D, heads, head_dim, mlp, span, ctx, cross_mask, mod_offset, slots = scalars
         assert (layers, T, D, heads, head_dim, mlp, ctx) == (16, 17, 1536, 32, 48, 6144, 300)
@@ -57,10 +57,16 @@ def test_block_kernel_recipe_is_one_launch_per_denoising_step():
     # each launch gets its own grid-wide arrival counter, inside the per-run area the prologue clears
     counters = [l["arguments"][7]["arena_offset"] for l in blocks]
     assert len(set(counters)) == cfg.steps and all(64 <= c < 1024 for c in counters)
-    # the tiny shape is covered too; a shape outside the kernel's limits falls back to separate launches
-    assert any(l["kernel"].startswith("agi_coop_dit_blocks") for l in dit.build_recipe(TINY).plan()["shape_dispatch"][0]["launches"])
+    # the tiny shape is covered too
+    assert any(l["kernel"].startswith("agi_coop_dit_blocks")
+               for l in dit.build_recipe(TINY, block_kernel=True).plan()["shape_dispatch"][0]["launches"])
+    # a shape outside the kernel's limits is refused, not silently built differently
     wide = dit.DitConfig(layers=2, hidden=2048, heads=32, head_dim=64, mlp=4096)
-    assert not any(l["kernel"].startswith("agi_coop") for l in dit.build_recipe(wide).plan()["shape_dispatch"][0]["launches"])
+    try:
+        dit.build_recipe(wide, block_kernel=True)
+        raise AssertionError("expected a ValueError")
+    except ValueError:
+        pass
 
 
 def test_oracle_runs_and_is_deterministic_on_a_tiny_shape():
