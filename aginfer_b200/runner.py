@@ -37,9 +37,21 @@ class Runner:
         return {t.name: torch.empty(t.shape, dtype=getattr(torch, TORCH_DTYPES[t.dtype]), device=device)
                 for t in self.outputs}
 
-    def run(self, inputs: Mapping[str, "object"], outputs: Mapping[str, "object"] | None = None, stream=None) -> dict:
+    def run(self, inputs: Mapping[str, "object"], outputs: Mapping[str, "object"] | None = None, stream=None,
+            denoising_steps: int = 0, noise_override=None) -> dict:
+        """``denoising_steps`` / ``noise_override`` (a tensor) travel as the reference's RunOptions: another
+        number of Euler steps runs the package's sibling profile for it, and the override replaces the ``noise``
+        input (which may then be left out of ``inputs``)."""
         import torch
         outputs = dict(outputs) if outputs is not None else self.empty_outputs()
+        options = None
+        if denoising_steps or noise_override is not None:
+            view = None
+            if noise_override is not None:
+                dtype = {t.name: t.dtype for t in self.inputs}.get("noise")
+                view = rt.TensorView.from_torch("noise_override", noise_override, dtype)
+                self._override_keep = noise_override
+            options = rt.run_options(denoising_steps, view)
         key = tuple(t.data_ptr() for t in inputs.values()) + tuple(t.data_ptr() for t in outputs.values())
         if key != self._packed_key:
             dt = {t.name: t.dtype for t in self.inputs + self.outputs}
@@ -55,10 +67,10 @@ class Runner:
             if self._side is None:
                 self._side = torch.cuda.Stream()
             self._side.wait_stream(s)
-            self.session.enqueue_packed(self._packed, self._side.cuda_stream)
+            self.session.enqueue_packed(self._packed, self._side.cuda_stream, options)
             s.wait_stream(self._side)
         else:
-            self.session.enqueue_packed(self._packed, s.cuda_stream)
+            self.session.enqueue_packed(self._packed, s.cuda_stream, options)
         return outputs
 
     def stats(self) -> dict:

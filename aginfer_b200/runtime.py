@@ -50,6 +50,11 @@ class _TensorInfo(C.Structure):
                 ("byte_size", C.c_uint64)]
 
 
+class _RunOptions(C.Structure):
+    _fields_ = [("denoising_steps", C.c_uint32), ("deterministic", C.c_uint32), ("seed", C.c_uint64),
+                ("math_mode", C.c_uint32), ("reserved", C.c_uint32), ("initial_noise_override", C.POINTER(_TensorView))]
+
+
 class _Stats(C.Structure):
     _fields_ = [("enqueues", C.c_uint64), ("kernel_launches", C.c_uint64), ("graph_launches", C.c_uint64),
                 ("graphs_built", C.c_uint64), ("launches_per_enqueue", C.c_uint64), ("upload_seconds", C.c_double)]
@@ -262,12 +267,15 @@ class Session:
         """Pre-pack views for repeated ``enqueue_packed`` calls (keeps ctypes work out of a timed loop)."""
         return _pack_views(inputs), _pack_views(outputs)
 
-    def enqueue_packed(self, packed, stream: int = 0) -> None:
+    def enqueue_packed(self, packed, stream: int = 0, options=None) -> None:
+        """``options``: a ``run_options(...)`` value, or None for the session's profile as packaged."""
         (ins, n_in, _), (outs, n_out, _) = packed
-        _check(load_library().agi_session_enqueue(self._h, ins, n_in, outs, n_out, None, C.c_void_p(stream)))
+        raw = C.byref(options[0]) if options is not None else None
+        _check(load_library().agi_session_enqueue(self._h, ins, n_in, outs, n_out, raw, C.c_void_p(stream)))
 
-    def enqueue(self, inputs: Iterable[TensorView], outputs: Iterable[TensorView], stream: int = 0) -> None:
-        self.enqueue_packed(self.bind(inputs, outputs), stream)
+    def enqueue(self, inputs: Iterable[TensorView], outputs: Iterable[TensorView], stream: int = 0,
+                options=None) -> None:
+        self.enqueue_packed(self.bind(inputs, outputs), stream, options)
 
     def stats(self) -> dict[str, float]:
         out = _Stats()
@@ -306,3 +314,19 @@ def gemm_bf16_static_scratch_status(out_ptr: int, stream: int = 0) -> None:
     """``agi_gemm_bf16_static_scratch_status``: copy the wait-status word of the last static-scratch GEMM
     into the caller's 4-byte device (or pinned host) word at ``out_ptr``, ordered on ``stream``."""
     _check(load_library().agi_gemm_bf16_static_scratch_status(C.c_void_p(out_ptr), C.c_void_p(stream)))
+
+
+
+def run_options(denoising_steps: int = 0, initial_noise_override: TensorView | None = None, seed: int = 0,
+                deterministic: bool = False, math_mode: int = 0):
+    """The reference's RunOptions (include/aginfer/runtime.h:84-90) for ``Session.enqueue``: ``denoising_steps``
+    selects the sibling profile ``<profile>/steps=<n>`` (0 = the session's profile as packaged) and
+    ``initial_noise_override`` stands in for the input named ``noise``; the other fields are carried and have
+    no effect.  Returns an opaque value that keeps the ctypes storage alive."""
+    raw = _RunOptions(denoising_steps, int(deterministic), seed, math_mode, 0, None)
+    keep = None
+    if initial_noise_override is not None:
+        array, _, keep = _pack_views([initial_noise_override])
+        raw.initial_noise_override = C.cast(array, C.POINTER(_TensorView))
+        keep = (array, keep)
+    return raw, keep

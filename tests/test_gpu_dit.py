@@ -61,3 +61,28 @@ def test_full_size_action_chunk_matches_oracle(tmp_path, block_kernel):
     # a fresh session reproduces the chunk bit for bit: partial sums are added in a fixed order
     again, _ = run_chunk(tmp_path / "again", cfg, w, x, repeats=1, block_kernel=block_kernel)
     assert torch.equal(again, got)
+
+
+def test_run_options_pick_the_step_count_and_the_noise(tmp_path):
+    # reference: RunOptions.denoising_steps / initial_noise_override (include/aginfer/runtime.h:84-90)
+    from dataclasses import replace
+    cfg = TINY
+    w, x = dit.synthetic_weights(cfg), dit.synthetic_inputs(cfg)
+    recipe = dit.build_recipe(cfg, step_profiles=(1, 4))
+    aim = build_aim(tmp_path, w, recipe, steps=cfg.steps, action_horizon=cfg.horizon, state_length=cfg.state_dim)
+    runner = Runner(aim)
+    dev = {k: v.cuda() for k, v in x.items()}
+    out = runner.empty_outputs()
+    other_noise = torch.randn(cfg.horizon, cfg.action_dim, generator=torch.Generator().manual_seed(99)).to(torch.bfloat16)
+    for steps, noise in ((0, None), (1, None), (4, None), (4, other_noise), (0, other_noise)):
+        runner.run(dev, out, denoising_steps=steps, noise_override=None if noise is None else noise.cuda())
+        torch.cuda.synchronize()
+        assert int(out["status"].item()) == 0
+        want = oracle_dit.forward(replace(cfg, steps=steps or cfg.steps), w, x["backbone_features"], x["state"],
+                                  x["noise"] if noise is None else noise)
+        got = out["actions"].cpu()
+        assert ops.cosine(got, want) >= 0.999 and ops.max_rel_err(got, want) < 2e-2, (steps, noise is not None)
+    # each step count keeps its own graph; a count the package does not carry is refused, not approximated
+    assert runner.stats()["graphs_built"] >= 3
+    with pytest.raises(rt.RuntimeStatusError, match="no recipe for 3 denoising steps"):
+        runner.run(dev, out, denoising_steps=3)

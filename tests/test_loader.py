@@ -157,3 +157,78 @@ def test_sm100_package_loads_and_reports(tmp_path):
         session.enqueue([good, good], [out])
     with pytest.raises(rt.RuntimeStatusError, match="no exact sm120"):
         rt.Session.create(rt.Runtime.create(cuda_arch_override=120, **OVERRIDES), model)
+
+
+def _steps_package(tmp_path):
+    """A package whose plan carries a profile, two step-count siblings of it and one malformed sibling."""
+    import aginfer_b200 as agi
+    from tests.test_packager import fake_cubin
+    io_in = [{"name": "state", "dtype": "BF16", "shape": [1, 64]}, {"name": "noise", "dtype": "BF16", "shape": [16, 32]}]
+    io_out = [{"name": "actions", "dtype": "F32", "shape": [16, 32]}]
+    launch = {"kernel": "k", "grid": [1, 1, 1], "block": [32, 1, 1], "arguments": [{"tensor": "noise"}, {"tensor": "actions"}]}
+
+    def profile(name, launches, outputs=io_out):
+        return {"profile": name, "inputs": io_in, "outputs": outputs, "launches": [launch] * launches}
+
+    plan = agi.compile_execution_plan({
+        "cuda_arch": "sm100", "arena_bytes": 1024, "workspace_bytes": 0,
+        "shape_dispatch": [profile("default", 4), profile("default/steps=2", 2), profile("default/steps=8", 8),
+                           profile("default/steps=3", 3, [{"name": "actions", "dtype": "F32", "shape": [8, 32]}]),
+                           profile("other", 1),
+                           {"profile": "plain", "inputs": io_in[:1], "outputs": io_out,
+                            "launches": [{**launch, "arguments": [{"tensor": "state"}, {"tensor": "actions"}]}]}],
+        "cuda_graph_templates": []}, agi.CudaArch.SM100, weight_size=8)
+    manifest = {"toolchain": {"cuda_driver_min": 12080, "cuda_runtime_min": 12080, "cuda_runtime_max": 12999,
+                              "cublaslt_abi": 12, "cudnn_abi": 9}}
+    path = tmp_path / "steps.aim"
+    agi.AimWriter.write(path, platform=agi.Platform.LINUX_X86_64_GNU, manifest=manifest, graph={}, tensors={},
+                        variants=[agi.VariantPayload(agi.CudaArch.SM100, fake_cubin(100, True), b"w" * 8, plan.data)])
+    return rt.Model.load(path)
+
+
+def test_run_options_select_a_step_count_profile_and_override_the_noise(tmp_path):
+    # reference: RunOptions (include/aginfer/runtime.h:84-90) are accepted and ignored (cpp/runtime.cc:499-500);
+    # here denoising_steps and initial_noise_override select work.  Everything below is decided before the first
+    # CUDA call, so it shows on a machine without a GPU: a call that passes validation ends in CUDA_ERROR here.
+    model = _steps_package(tmp_path)
+    session = rt.Session.create(rt.Runtime.create(cuda_arch_override=100, **OVERRIDES), model, "default")
+    buf = ctypes.create_string_buffer(16 * 32 * 4)
+    state = rt.TensorView("state", "BF16", (1, 64), (64, 1), ctypes.addressof(buf), 128)
+    noise = rt.TensorView("noise", "BF16", (16, 32), (32, 1), ctypes.addressof(buf), 1024)
+    actions = rt.TensorView("actions", "F32", (16, 32), (32, 1), ctypes.addressof(buf), 2048)
+
+    def outcome(inputs, options):
+        with pytest.raises(rt.RuntimeStatusError) as caught:
+            session.enqueue(inputs, [actions], options=options)
+        return caught.value.name, str(caught.value)
+
+    assert outcome([state, noise], None)[0] == "CUDA_ERROR"                      # validated, then no driver
+    assert session.stats()["launches_per_enqueue"] == 4
+    assert outcome([state, noise], rt.run_options(2))[0] == "CUDA_ERROR"
+    assert session.stats()["launches_per_enqueue"] == 2                          # the sibling profile was selected
+    assert outcome([state, noise], rt.run_options(8, seed=7, deterministic=True))[0] == "CUDA_ERROR"
+    assert session.stats()["launches_per_enqueue"] == 8
+    name, text = outcome([state, noise], rt.run_options(5))
+    assert name == "INVALID_ARGUMENT" and "no recipe for 5 denoising steps" in text and "default/steps=5" in text
+    name, text = outcome([state, noise], rt.run_options(3))
+    assert name == "CORRUPT_PACKAGE" and "does not have the tensors" in text
+    assert outcome([state, noise], rt.run_options(0))[0] == "CUDA_ERROR"
+    assert session.stats()["launches_per_enqueue"] == 4
+
+    # the override stands in for "noise": with or without a "noise" among the inputs, under any name of its own
+    override = rt.TensorView("whatever", "BF16", (16, 32), (32, 1), ctypes.addressof(buf), 1024)
+    assert outcome([state], rt.run_options(0, override))[0] == "CUDA_ERROR"
+    assert outcome([state, noise], rt.run_options(2, override))[0] == "CUDA_ERROR"
+    # ... and is validated like any other view
+    short = rt.TensorView("noise", "BF16", (8, 32), (32, 1), ctypes.addressof(buf), 1024)
+    name, text = outcome([state], rt.run_options(0, short))
+    assert name == "INVALID_ARGUMENT" and "shape or stride" in text
+    name, text = outcome([state], None)
+    assert name == "INVALID_ARGUMENT" and "count does not match" in text
+    # a profile without step-count siblings, or without an input named "noise", says so
+    other = rt.Session.create(rt.Runtime.create(cuda_arch_override=100, **OVERRIDES), model, "other")
+    with pytest.raises(rt.RuntimeStatusError, match="no recipe for 2 denoising steps"):
+        other.enqueue([state, noise], [actions], options=rt.run_options(2))
+    plain = rt.Session.create(rt.Runtime.create(cuda_arch_override=100, **OVERRIDES), model, "plain")
+    with pytest.raises(rt.RuntimeStatusError, match="no input named noise"):
+        plain.enqueue([state], [actions], options=rt.run_options(0, override))
