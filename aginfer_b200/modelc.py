@@ -230,6 +230,66 @@ def compile_model(options: CompileOptions) -> AimInfo:
                            tensors={"alignment": 256, "count": len(table), "items": table}, variants=variants)
 
 
+def plan_artifacts(args) -> dict[str, Any]:
+    """``modelc plan``: checkpoint directory + adapter + shape profile -> ``<artifact-dir>/toolchain.json`` and
+    ``<artifact-dir>/sm100/{kernels.cubin,plan.json,tactics.json}``, ready for ``modelc compile``.  The role the
+    reference leaves to whoever fills ``--artifact-dir`` (``src/aginfer/compiler.py:61-75``), driven by the
+    adapter's graph description (``src/aginfer/adapters/groot.py:13-29``)."""
+    from .recipes import lowering
+    if args.cuda_arch != CudaArch.SM100:
+        raise ValidationError("modelc plan generates sm100 recipes only")
+    profile = load_profile(args.profile)
+    source = args.source
+    if args.pack_checkpoint:
+        source = str(_pack_checkpoint(Path(args.source), args.pack_checkpoint))
+    checkpoint = load_checkpoint(source, None, args.offline)
+    _, graph = describe_model(args.adapter, checkpoint)
+    tensors = list(checkpoint.tensors)
+    if args.backbone:
+        taken = {t.name for t in tensors}
+        tensors += [replace(t, name=f"backbone.{t.name}") if t.name in taken else t
+                    for t in load_checkpoint(args.backbone, None, args.offline).tensors]
+    inventory = {t.name: (t.dtype, tuple(t.shape)) for t in tensors}
+    steps = tuple(int(v) for v in args.step_profiles.split(",") if v.strip())
+    recipe, name, shape = lowering.lower(args.adapter, graph, inventory, checkpoint.config, profile,
+                                         packed=bool(args.packed or args.pack_checkpoint), step_profiles=steps,
+                                         heads=args.heads)
+    lowering.write_artifact_dir(args.artifact_dir, recipe)
+    plan = recipe.plan()
+    return {"artifact_dir": str(args.artifact_dir), "recipe": name, "source": source, "shape": shape,
+            "profiles": {p["profile"]: len(p["launches"]) for p in plan["shape_dispatch"]},
+            "arena_bytes": plan["arena_bytes"], "weight_bytes": recipe.weight_bytes,
+            "graph_passes": list(graph["passes"])}
+
+
+def _pack_checkpoint(source: Path, target: Path) -> Path:
+    """The packaging-time layout pass for FP8 prefill recipes: every E4M3 ``[N, K]`` linear weight rewritten into
+    the packed tile layout of ``recipes/layout.py`` (same names; shape [K / 128, N padded to 256, 128]); everything else copied."""
+    import shutil
+
+    import torch
+
+    from .recipes import qwen_vl
+    from .recipes.package import tensor_record
+    from .weights import write_safetensors
+    checkpoint = load_checkpoint(str(source), None, True)
+    target.mkdir(parents=True, exist_ok=True)
+    for path in sorted(Path(source).iterdir()):
+        if path.is_file() and path.suffix != ".safetensors":
+            shutil.copy(path, target / path.name)
+    dtypes = {"F32": torch.float32, "F16": torch.float16, "BF16": torch.bfloat16, "F8_E4M3": torch.float8_e4m3fn}
+    by_file: dict[Path, dict[str, Any]] = {}
+    for record in checkpoint.tensors:
+        with open(record.source, "rb") as handle:
+            handle.seek(record.source_offset)
+            data = torch.frombuffer(bytearray(handle.read(record.byte_length)), dtype=torch.uint8)
+        by_file.setdefault(record.source, {})[record.name] = data.view(dtypes[record.dtype]).reshape(record.shape)
+    for path, tensors in by_file.items():
+        packed = qwen_vl.pack_checkpoint(tensors)
+        write_safetensors(target / path.name, {k: tensor_record(v) for k, v in packed.items()})
+    return target
+
+
 def _typed(parser):
     def convert(text: str):
         try:
@@ -255,6 +315,23 @@ def build_parser() -> argparse.ArgumentParser:
     c.add_argument("--backbone", help="local Qwen2.5-VL checkpoint required by lingbot_vla_1")
     c.add_argument("--offline", action="store_true")
     c.add_argument("--output", required=True, type=Path)
+    g = sub.add_parser("plan", help="write the sm100 artifact directory (kernel bundle, plan.json, tactics.json, "
+                                    "toolchain.json) for a checkpoint: the adapter's graph passes lowered to a launch recipe")
+    g.add_argument("--source", required=True)
+    g.add_argument("--adapter", required=True, choices=adapter_names())
+    g.add_argument("--profile", required=True, type=Path)
+    g.add_argument("--cuda-arch", required=True, type=_typed(CudaArch.parse), dest="cuda_arch")
+    g.add_argument("--artifact-dir", required=True, type=Path)
+    g.add_argument("--backbone", help="local Qwen2.5-VL checkpoint whose tensors join the blob (lingbot_vla_1)")
+    g.add_argument("--packed", action="store_true",
+                   help="FP8 linear weights are in the packed tile layout (see --pack-checkpoint)")
+    g.add_argument("--pack-checkpoint", type=Path, metavar="DIR",
+                   help="first rewrite the checkpoint's FP8 linear weights into the packed tile layout under DIR "
+                        "(same tensor names) and plan for that copy; implies --packed")
+    g.add_argument("--step-profiles", default="", help="comma-separated extra Euler step counts to package as "
+                                                       "sibling profiles <profile>/steps=<n>")
+    g.add_argument("--heads", type=int, help="attention heads of the action head when config.json does not say")
+    g.add_argument("--offline", action="store_true")
     i = sub.add_parser("inspect", help="verify and display an AIM manifest")
     i.add_argument("aim", type=Path)
     i.add_argument("--no-payload-checksums", action="store_true")
@@ -270,6 +347,9 @@ def main(argv: list[str] | None = None) -> int:
                 cuda_arches=tuple(args.cuda_arches), profile_path=args.profile, artifact_dir=args.artifact_dir,
                 output=args.output, offline=args.offline, backbone=args.backbone))
             print(f"wrote {info.path} ({info.file_size} bytes, sha256={info.file_sha256})")
+            return 0
+        if args.command == "plan":
+            print(json.dumps(plan_artifacts(args), sort_keys=True))
             return 0
         info = AimReader.read(args.aim, verify_payloads=not args.no_payload_checksums)
         print(json.dumps({

@@ -37,10 +37,16 @@ def describe(tensors: Mapping[str, Any]) -> dict[str, tuple[str, tuple[int, ...]
     return {k: (names[v.dtype], tuple(v.shape)) for k, v in tensors.items()}
 
 
-def write_checkpoint(root: Path, tensors: Mapping[str, Any], model_type: str = "groot") -> Path:
+def write_checkpoint(root: Path, tensors: Mapping[str, Any], model_type: str = "groot",
+                     recipe: tuple[str, Any] | None = None) -> Path:
+    """``recipe``: (generator name, its config dataclass), recorded in ``config.json`` under ``aginfer_recipe`` so
+    that ``modelc plan`` can rebuild the launch recipe from the checkpoint directory alone."""
     import torch
     root.mkdir(parents=True, exist_ok=True)
     config: dict[str, Any] = {"model_type": model_type, "architectures": ["SyntheticForActionPrediction"]}
+    if recipe is not None:
+        import dataclasses
+        config["aginfer_recipe"] = {"name": recipe[0], "config": json.loads(json.dumps(dataclasses.asdict(recipe[1])))}
     if any(t.dtype == torch.float8_e4m3fn for t in tensors.values()):
         config["quantization_config"] = dict(FP8_CONFIG)
     (root / "config.json").write_text(json.dumps(config))
