@@ -27,16 +27,20 @@ extern "C" __global__ void agi_rope_bf16(bf16* x, unsigned rows, unsigned heads,
 
 // Multimodal RoPE: three position streams (temporal, height, width) given as int32
 // pos[3][rows]; rotary pair i takes its position from stream 0 for i < s0, stream 1 for
-// i < s0 + s1, else stream 2 (sections (16, 24, 24) for head_dim 128).
+// i < s0 + s1, else stream 2 (sections (16, 24, 24) for head_dim 128).  `ladder` = rotary pairs per frequency
+// ladder: pair i turns at theta^(-(i mod ladder) / ladder).  head_dim / 2 gives the one ladder of a language
+// model; the vision tower's 2-D rotary uses head_dim / 4: one ladder for the rows, the same one again for the
+// columns.
 extern "C" __global__ void agi_mrope_bf16(bf16* x, const int* pos, unsigned rows, unsigned heads, unsigned head_dim,
-                                           unsigned row_stride, float log2_theta, unsigned s0, unsigned s1) {
+                                           unsigned row_stride, float log2_theta, unsigned s0, unsigned s1,
+                                           unsigned ladder) {
   grid_dependency_wait();
   const unsigned half = head_dim / 2;
   const unsigned total = rows * heads * half;
   for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
     const unsigned pair = i % half, head = (i / half) % heads, row = i / (half * heads);
     const unsigned stream = pair < s0 ? 0u : (pair < s0 + s1 ? 1u : 2u);
-    const float inv_freq = exp2f(-log2_theta * (2.f * float(pair) / float(head_dim)));
+    const float inv_freq = exp2f(-log2_theta * (float(pair % ladder) / float(ladder)));
     float s, c;
     sincosf(float(pos[stream * rows + row]) * inv_freq, &s, &c);
     bf16* p = x + size_t(row) * row_stride + head * head_dim + pair;

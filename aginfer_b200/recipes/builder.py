@@ -419,12 +419,14 @@ class RecipeBuilder:
                     op="rope")
 
     def mrope(self, x: Pointer, positions: Pointer, rows: int, heads: int, head_dim: int, row_stride: int,
-              theta: float, sections: Sequence[int]) -> None:
+              theta: float, sections: Sequence[int], ladder: int | None = None) -> None:
+        """``ladder``: rotary pairs per frequency ladder (pair i turns at theta^(-(i mod ladder) / ladder));
+        default head_dim / 2, the single ladder of a language model."""
         assert sum(sections) == head_dim // 2 and len(sections) == 3
         work = rows * heads * head_dim // 2
         self.launch("agi_mrope_bf16", (grid_for(work), 1, 1), (256, 1, 1),
                     [x, positions, U32(rows), U32(heads), U32(head_dim), U32(row_stride), F32(math.log2(theta)),
-                     U32(sections[0]), U32(sections[1])], op="mrope")
+                     U32(sections[0]), U32(sections[1]), U32(ladder or head_dim // 2)], op="mrope")
 
     def attention(self, q: Pointer, k: Pointer, v: Pointer, o: Pointer, *, q_rows: int, kv_rows: int, q_heads: int,
                   kv_heads: int, head_dim: int, q_stride: int, k_stride: int, v_stride: int, o_stride: int,

@@ -11,7 +11,8 @@ What the shape description leaves open is fixed here and mirrored by the CPU ora
   * tokens run in window order from the patch gather on (see csrc/kernels/vision.cuh); merged tokens return to
     raster order when they are written into the language model's hidden states;
   * vision rotary embedding: half-split pairs over the 80-wide head, the first 20 pairs turn with the patch
-    row, the last 20 with the patch column, frequencies theta^(-2i/80), theta = 10000;
+    row, the last 20 with the patch column, each group over the same frequency ladder theta^(-j/20), j = 0..19,
+    theta = 10000 (the published Qwen2.5-VL vision rotary);
   * all vision linears carry a bias; in the language model only q/k/v do;
   * merger = RMSNorm(1280) -> concat of the 4 patches of a group -> Linear + GELU(tanh) -> Linear;
   * image tokens come first in the prefix (image 0, image 1), then the text tokens; M-RoPE positions are an
@@ -290,7 +291,7 @@ def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto", trace: bool 
         norm_quantize(x, f"{b}.norm1.weight", normed, P, VH)
         linear_q(f"{b}.attn.qkv", qkv, P, 3 * VH, VH)
         # rows x (q heads + k heads) of width 80 sit side by side at the start of each qkv row
-        r.mrope(qkv, vpos, P, 2 * cfg.v_heads, VD, 3 * VH, cfg.v_theta, (half // 2, half - half // 2, 0))
+        r.mrope(qkv, vpos, P, 2 * cfg.v_heads, VD, 3 * VH, cfg.v_theta, (half // 2, half - half // 2, 0), ladder=half // 2)
         span = cfg.grid * cfg.grid if i in cfg.v_full_layers else cfg.window * cfg.window
         r.attention(qkv, qkv + VH * BF, qkv + 2 * VH * BF, attn, q_rows=P, kv_rows=P, q_heads=cfg.v_heads,
                     kv_heads=cfg.v_heads, head_dim=VD, q_stride=3 * VH, k_stride=3 * VH, v_stride=3 * VH, o_stride=VH,

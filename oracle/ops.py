@@ -81,11 +81,15 @@ def rope(x: torch.Tensor, theta: float, pos_offset: int = 0) -> torch.Tensor:
     return _rotate(x, pos[:, None] * inv_freq[None, :])
 
 
-def mrope(x: torch.Tensor, positions: torch.Tensor, theta: float, sections: tuple[int, int, int]) -> torch.Tensor:
+def mrope(x: torch.Tensor, positions: torch.Tensor, theta: float, sections: tuple[int, int, int],
+          ladder: int | None = None) -> torch.Tensor:
     """Multimodal rotary embedding: positions [3, rows] (temporal, height, width); rotary pair i uses
-    stream 0 for i < s0, stream 1 for i < s0 + s1, else stream 2."""
+    stream 0 for i < s0, stream 1 for i < s0 + s1, else stream 2, and turns at theta^(-(i mod ladder) / ladder).
+    ``ladder`` defaults to d / 2 (one frequency ladder over all pairs, as in a language model); a vision tower's
+    2-D rotary has d / 4: the same ladder for the row half and for the column half of the pairs."""
     rows, _, d = x.shape
-    inv_freq = theta ** (-torch.arange(0, d, 2, dtype=torch.float32) / d)
+    ladder = ladder or d // 2
+    inv_freq = theta ** (-(torch.arange(d // 2, dtype=torch.float32) % ladder) / ladder)
     stream = torch.repeat_interleave(torch.arange(3), torch.tensor(sections))
     pos = positions.float()[stream, :].t()  # [rows, d/2]
     return _rotate(x, pos * inv_freq[None, :])

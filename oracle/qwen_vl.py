@@ -70,7 +70,7 @@ def vision_block(cfg, w: dict, i: int, x: torch.Tensor, pos: torch.Tensor) -> to
     b = f"visual.blocks.{i}"
     xq, xs = ops.quantize_e4m3(ops.rmsnorm(x, w[f"{b}.norm1.weight"], cfg.eps))
     qkv = _fp8_linear(w, f"{b}.attn.qkv", xq, xs)
-    qk = ops.mrope(qkv[:, :2 * VH].reshape(P, 2 * cfg.v_heads, VD), pos, cfg.v_theta, sections)
+    qk = ops.mrope(qkv[:, :2 * VH].reshape(P, 2 * cfg.v_heads, VD), pos, cfg.v_theta, sections, ladder=half // 2)
     q, k = qk[:, :cfg.v_heads], qk[:, cfg.v_heads:]
     v = qkv[:, 2 * VH:].reshape(P, cfg.v_heads, VD)
     span = cfg.grid * cfg.grid if i in cfg.v_full_layers else cfg.window * cfg.window
