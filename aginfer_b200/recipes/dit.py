@@ -139,14 +139,29 @@ def build_recipe(cfg: DitConfig = DitConfig(), weights: Mapping[str, tuple[str, 
     return r
 
 
-def _emit_chunk(r: RecipeBuilder, cfg: DitConfig, profile: str, gemm_tactic: str, fuse: bool, batch_kv: bool,
-                block_kernel: bool, measure: bool) -> None:
-    """One profile: the whole action chunk of ``cfg.steps`` Euler steps."""
+def head_inputs(cfg: DitConfig) -> list[dict]:
+    """The profile inputs the action head reads besides the context tokens."""
+    return [io("state", "BF16", [1, cfg.state_dim]), io("noise", "BF16", [cfg.horizon, cfg.action_dim])]
+
+
+def emit_action_head(r: RecipeBuilder, cfg: DitConfig, context, *, gemm_tactic: str = "auto", fuse: bool = True,
+                     batch_kv: bool = True, block_kernel: bool = False) -> None:
+    """Append the whole action chunk to the profile being built: ``context`` ([backbone_tokens, backbone_dim] bf16,
+    any pointer: a profile input, or what an earlier part of the same profile wrote) conditions the head, which
+    reads the profile tensors ``state`` and ``noise`` and writes ``actions``."""
+    _emit_chunk(r, cfg, None, gemm_tactic, fuse, batch_kv, block_kernel, measure=False, context=context)
+
+
+def _emit_chunk(r: RecipeBuilder, cfg: DitConfig, profile: str | None, gemm_tactic: str, fuse: bool, batch_kv: bool,
+                block_kernel: bool, measure: bool, context=None) -> None:
+    """One profile: the whole action chunk of ``cfg.steps`` Euler steps (``profile`` None: appended to the
+    profile that is already open, without a status export of its own)."""
     D, T, H, S = cfg.hidden, cfg.tokens, cfg.horizon, cfg.steps
-    r.begin_profile(profile, [io("backbone_features", "BF16", [cfg.backbone_tokens, cfg.backbone_dim]),
-                              io("state", "BF16", [1, cfg.state_dim]),
-                              io("noise", "BF16", [H, cfg.action_dim])],
-                    [io("actions", "F32", [H, cfg.action_dim]), io("status", "I32", [1])])
+    if profile is not None:
+        r.begin_profile(profile, [io("backbone_features", "BF16", [cfg.backbone_tokens, cfg.backbone_dim]),
+                                  *head_inputs(cfg)],
+                        [io("actions", "F32", [H, cfg.action_dim]), io("status", "I32", [1])])
+    context = context if context is not None else Tensor("backbone_features")
     BF = 2
 
     def lin(x, name, y, M, N, K, **kw):
@@ -176,13 +191,13 @@ def _emit_chunk(r: RecipeBuilder, cfg: DitConfig, profile: str, gemm_tactic: str
         jobs = [(Weight(f"{P}.dit.blocks.{l}.attn.{n}.weight"), Weight(f"{P}.dit.blocks.{l}.attn.{n}.bias"))
                 for l in cross for n in ("to_k", "to_v")]
         for i in range(0, len(jobs), 16):
-            r.gemm_batch(Tensor("backbone_features"), jobs[i:i + 16], kv_all + i * kv_bytes, cfg.backbone_tokens, D,
+            r.gemm_batch(context, jobs[i:i + 16], kv_all + i * kv_bytes, cfg.backbone_tokens, D,
                          cfg.backbone_dim, seg_stride=cfg.backbone_tokens * D)
     else:
         for l, (k_buf, v_buf) in kv.items():
             b = f"{P}.dit.blocks.{l}.attn"
-            lin(Tensor("backbone_features"), f"{b}.to_k", k_buf, cfg.backbone_tokens, D, cfg.backbone_dim)
-            lin(Tensor("backbone_features"), f"{b}.to_v", v_buf, cfg.backbone_tokens, D, cfg.backbone_dim)
+            lin(context, f"{b}.to_k", k_buf, cfg.backbone_tokens, D, cfg.backbone_dim)
+            lin(context, f"{b}.to_v", v_buf, cfg.backbone_tokens, D, cfg.backbone_dim)
     t_sin, t_hid, temb, temb_act = (r.alloc(S * cfg.time_dim * BF), r.alloc(S * D * BF), r.alloc(S * D * BF),
                                     r.alloc(S * D * BF))
     times = cfg.step_times()
@@ -274,7 +289,8 @@ def _emit_chunk(r: RecipeBuilder, cfg: DitConfig, profile: str, gemm_tactic: str
 
     r.launch("agi_copy_u32", (1, 1, 1), (256, 1, 1), [x_f32, Tensor("actions"), U32(H * cfg.action_dim)],
              op="copy_out")
-    r.export_status(Tensor("status"))   # 0 = every bounded wait of the chunk was satisfied
+    if profile is not None:
+        r.export_status(Tensor("status"))   # 0 = every bounded wait of the chunk was satisfied
 
     if measure and block_kernel:
         # Measurement profiles of the persistent block kernel: the pointer table plus 1 resp. 5 launches of one

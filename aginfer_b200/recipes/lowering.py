@@ -21,7 +21,7 @@ from pathlib import Path
 from typing import Any, Mapping, Sequence
 
 from ..errors import ValidationError
-from . import decoder_layer, dit, lingbot, qwen_vl
+from . import decoder_layer, dit, lingbot, qwen_vl, vla
 from .builder import RecipeBuilder
 
 Inventory = Mapping[str, tuple[str, tuple[int, ...]]]      # tensor name -> (dtype, shape)
@@ -50,6 +50,8 @@ def config_from_dict(cls, values: Mapping[str, Any]):
     built = {}
     for key, value in values.items():
         default = fields[key].default
+        if default is dataclasses.MISSING and fields[key].default_factory is not dataclasses.MISSING:
+            default = fields[key].default_factory()
         if dataclasses.is_dataclass(default) and isinstance(value, Mapping):
             value = config_from_dict(type(default), value)
         elif isinstance(default, tuple) and isinstance(value, list):
@@ -102,8 +104,8 @@ def choose_recipe(adapter: str, graph: Mapping[str, Any], inventory: Inventory, 
     has_backbone = any(n.startswith(("visual.", "model.")) for n in inventory)
     if "pi_action_expert_step" in subgraphs and has_expert and has_backbone:
         return "lingbot_episode"
-    if "flow_matching_dit_step" in subgraphs and has_head and not has_backbone:
-        return "dit"
+    if "flow_matching_dit_step" in subgraphs and has_head:
+        return "vla" if has_backbone else "dit"       # with the backbone's tensors: pixels and ids in, actions out
     if has_backbone and not has_head and not has_expert:
         return "qwen_vl_prefill"
     raise ValidationError(f"no sm100 recipe generator for adapter {adapter} with this checkpoint's tensors")
@@ -121,6 +123,9 @@ def lower(adapter: str, graph: Mapping[str, Any], inventory: Inventory, config: 
     if name == "dit":
         cfg = config_from_dict(dit.DitConfig, values) if values else infer_dit_config(inventory, profile, heads)
         recipe = dit.build_recipe(cfg, inventory, fuse=fused, batch_kv="fuse_qkv" in passes, step_profiles=tuple(step_profiles))
+    elif name == "vla":
+        cfg = config_from_dict(vla.VlaConfig, values or {})
+        recipe = vla.build_recipe(cfg, inventory, packed=packed)
     elif name == "qwen_vl_prefill":
         cfg = config_from_dict(qwen_vl.VlConfig, values or {})
         recipe = qwen_vl.build_recipe(cfg, inventory, packed=packed)

@@ -26,6 +26,7 @@ status word (0 = every bounded wait in every kernel succeeded).
 from __future__ import annotations
 
 from dataclasses import dataclass, field
+from typing import Sequence
 
 from .builder import RecipeBuilder, Tensor, U32, Weight, ceil_div, grid_for, io
 from .layout import pack_kblock_swizzled, padded_token_rows
@@ -204,7 +205,7 @@ def synthetic_inputs(cfg: VlConfig, seed: int = 3) -> dict:
 
 def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto", trace: bool = False,
                  group: bool = True, packed: bool = False, extra_inputs=(), extra_outputs=(), tail=None,
-                 extra_counters: int = 0) -> RecipeBuilder:
+                 extra_counters: int = 0, operand_trace: Sequence[str] = ()) -> RecipeBuilder:
     """``weights``: name -> (dtype, shape) as from ``package.describe``.  ``trace`` adds three outputs for
     block-by-block checks: ``vision_trace`` [v_layers + 1, patches, 1280] (the patch embedding, then every
     block's output), ``merged_out`` [merged, hidden] (window order) and ``hidden_trace``
@@ -213,17 +214,27 @@ def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto", trace: bool 
     a checkpoint that went through ``pack_checkpoint``; activations are quantised into the same layout and every
     FP8 GEMM fills its ring with bulk copies.  ``tail(recipe, cache, hidden)`` appends launches that consume the
     prefill inside the same profile (an action expert reading the K/V cache), with ``extra_inputs`` /
-    ``extra_outputs`` added to the profile's interface."""
+    ``extra_outputs`` added to the profile's interface.  ``operand_trace`` (row-major operands only): names of
+    blocks (``visual.blocks.3``, ``model.layers.0`` ...) whose four quantised GEMM inputs are exported as they
+    stand in front of the GEMM: outputs ``<block>.operand<j>`` (E4M3 bytes [rows, K]) and ``<block>.scale<j>``
+    (fp32), j = 0..3 = after the first norm, after attention, after the second norm, after SwiGLU."""
     BF = 2
     P, VH, VD, VI = cfg.patches, cfg.v_hidden, cfg.v_head_dim, cfg.v_mlp_padded
     S, H, I, D = cfg.tokens, cfg.hidden, cfg.intermediate, cfg.head_dim
     G = cfg.grid // cfg.merge
+    assert not (operand_trace and packed), "operands are exported in the row-major layout only"
+    operand_shapes = {}
+    for block in operand_trace:
+        rows, ks = (P, (VH, VH, VH, VI)) if block.startswith("visual.") else (S, (H, cfg.q_dim, H, I))
+        operand_shapes[block] = [(rows, k) for k in ks]
+    operand_outputs = [spec for block, shapes in operand_shapes.items() for j, (rows, k) in enumerate(shapes)
+                       for spec in (io(f"{block}.operand{j}", "F8_E4M3", [rows, k]), io(f"{block}.scale{j}", "F32", [1]))]
     r = RecipeBuilder(weights, counter_slots=4 * (cfg.v_layers + cfg.layers) + 8 + extra_counters)   # one per quantisation
     r.begin_profile("default",
                     [io("pixels", "F32", [cfg.images, cfg.channels, cfg.image_size, cfg.image_size]),
                      io("input_ids", "I32", [cfg.text_tokens]), io("positions", "I32", [3, S]), *extra_inputs],
                     [io("hidden_out", "BF16", [S, H]), io("kv_cache", "BF16", [cfg.layers, 2, S, cfg.kv_dim]),
-                     io("status", "I32", [1]), *extra_outputs] + ([io("vision_trace", "BF16", [cfg.v_layers + 1, P, VH]),
+                     io("status", "I32", [1]), *extra_outputs, *operand_outputs] + ([io("vision_trace", "BF16", [cfg.v_layers + 1, P, VH]),
                                                    io("merged_out", "BF16", [cfg.merged, H]),
                                                    io("hidden_trace", "BF16", [cfg.layers + 1, S, H])] if trace else []))
     rows_of = padded_token_rows if packed else (lambda m: m)
@@ -239,8 +250,21 @@ def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto", trace: bool 
             r.launch("agi_copy_u32", (grid_for(nbytes // 4), 1, 1), (256, 1, 1), [src, keep, U32(nbytes // 4)], op="trace")
             traces.append((keep, name, index, nbytes))
 
+    watched: dict[str, int] = {}      # block being built -> quantisations seen so far (operand_trace only)
+
     def quantize(x, rows: int, K: int, amax=None):
         r.quantize_e4m3(x, quant, scale, rows * K, amax=amax, packed=(rows, K) if packed else None)
+        for block in watched:
+            j = watched[block]
+            r.launch("agi_copy_u32", (grid_for(rows * K // 4), 1, 1), (256, 1, 1),
+                     [quant, Tensor(f"{block}.operand{j}"), U32(rows * K // 4)], op="trace")
+            r.launch("agi_copy_u32", (1, 1, 1), (32, 1, 1), [scale, Tensor(f"{block}.scale{j}"), U32(1)], op="trace")
+            watched[block] = j + 1
+
+    def watch(block: str) -> None:
+        watched.clear()
+        if block in operand_shapes:
+            watched[block] = 0
 
     def norm_quantize(x, gain: str, y, rows: int, cols: int, q_rows: int | None = None, q_cols: int | None = None):
         """RMSNorm that also leaves max |y| behind, then the E4M3 quantisation of y (viewed [q_rows, q_cols])."""
@@ -288,6 +312,7 @@ def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto", trace: bool 
     half = VD // 2
     for i in range(cfg.v_layers):
         b = f"visual.blocks.{i}"
+        watch(b)
         norm_quantize(x, f"{b}.norm1.weight", normed, P, VH)
         linear_q(f"{b}.attn.qkv", qkv, P, 3 * VH, VH)
         # rows x (q heads + k heads) of width 80 sit side by side at the start of each qkv row
@@ -303,6 +328,7 @@ def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto", trace: bool 
         swiglu_quantize(gate_up, gate_up + VI * BF, act, P, VI)
         linear_q(f"{b}.mlp.down_proj", x, P, VH, VI, residual=x2)
         snapshot(x, "vision_trace", i + 1, P * VH * BF)
+    watch("")
     # merger: per-patch norm; four consecutive rows of 1280 are one row of 5120
     M4, MD = cfg.merged, cfg.merged_dim
     mid, merged = r.alloc(M4 * MD * BF), r.alloc(M4 * H * BF)
@@ -325,6 +351,7 @@ def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto", trace: bool 
     snapshot(h, "hidden_trace", 0, S * H * BF)
     for i in range(cfg.layers):
         l = f"model.layers.{i}"
+        watch(l)
         k_cache = cache + (2 * i) * S * cfg.kv_dim * BF
         v_cache = cache + (2 * i + 1) * S * cfg.kv_dim * BF
         norm_quantize(h, f"{l}.input_layernorm.weight", hn, S, H)
@@ -342,6 +369,7 @@ def build_recipe(cfg: VlConfig, weights, gemm_tactic: str = "auto", trace: bool 
         swiglu_quantize(gu, gu + I * BF, sw, S, I)
         linear_q(f"{l}.mlp.down_proj", h, S, H, I, residual=h2)
         snapshot(h, "hidden_trace", i + 1, S * H * BF)
+    watch("")
     r.rmsnorm(h, Weight("model.norm.weight"), Tensor("hidden_out"), S, H, cfg.eps)
     words = cfg.layers * 2 * S * cfg.kv_dim * BF // 4
     r.launch("agi_copy_u32", (grid_for(words), 1, 1), (256, 1, 1), [cache, Tensor("kv_cache"), U32(words)],

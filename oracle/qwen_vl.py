@@ -83,6 +83,28 @@ def vision_block(cfg, w: dict, i: int, x: torch.Tensor, pos: torch.Tensor) -> to
     return _fp8_linear(w, f"{b}.mlp.down_proj", aq, as_, residual=x2)
 
 
+def vision_block_forced(cfg, w: dict, i: int, x: torch.Tensor, pos: torch.Tensor, operands):
+    """``vision_block`` with every GEMM fed the quantised operands a device run used: ``operands`` = four
+    (E4M3 tensor [rows, K], fp32 scale) in the order they are produced.  Returns (block output, the oracle's own
+    tensors at the four quantisation points, each computed from the forced operands upstream of it).  Two correct
+    implementations then differ only by accumulation order and the bf16 rounding of the output, which is what
+    the 2e-2 tier is for; the per-tensor scale jitter of free-running FP8 is taken out."""
+    P, VH, VD = cfg.patches, cfg.v_hidden, cfg.v_head_dim
+    half = VD // 2
+    b = f"visual.blocks.{i}"
+    refs = [ops.rmsnorm(x, w[f"{b}.norm1.weight"], cfg.eps)]
+    qkv = _fp8_linear(w, f"{b}.attn.qkv", *operands[0])
+    qk = ops.mrope(qkv[:, :2 * VH].reshape(P, 2 * cfg.v_heads, VD), pos, cfg.v_theta, (half // 2, half - half // 2, 0),
+                   ladder=half // 2)
+    span = cfg.grid * cfg.grid if i in cfg.v_full_layers else cfg.window * cfg.window
+    refs.append(ops.attention(qk[:, :cfg.v_heads], qk[:, cfg.v_heads:], qkv[:, 2 * VH:].reshape(P, cfg.v_heads, VD),
+                              mask="block", mask_arg=span).reshape(P, VH))
+    x2 = _fp8_linear(w, f"{b}.attn.proj", *operands[1], residual=x)
+    refs.append(ops.rmsnorm(x2, w[f"{b}.norm2.weight"], cfg.eps))
+    refs.append(ops.swiglu(_fp8_linear(w, f"{b}.mlp.gate_proj", *operands[2]), _fp8_linear(w, f"{b}.mlp.up_proj", *operands[2])))
+    return _fp8_linear(w, f"{b}.mlp.down_proj", *operands[3], residual=x2), refs
+
+
 def merger(cfg, w: dict, x: torch.Tensor) -> torch.Tensor:
     """Patch tokens [patches, 1280] (window order) -> merged tokens [patches / 4, hidden] (window order)."""
     normed = ops.rmsnorm(x, w["visual.merger.ln_q.weight"], cfg.eps).reshape(cfg.merged, cfg.merged_dim)
@@ -120,6 +142,23 @@ def decoder_layer(cfg, w: dict, i: int, h: torch.Tensor, positions: torch.Tensor
     act = ops.swiglu(_fp8_linear(w, f"{l}.mlp.gate_proj", xq, xs), _fp8_linear(w, f"{l}.mlp.up_proj", xq, xs))
     aq, as_ = ops.quantize_e4m3(act)
     return _fp8_linear(w, f"{l}.mlp.down_proj", aq, as_, residual=h2), k.reshape(S, cfg.kv_dim), v.reshape(S, cfg.kv_dim)
+
+
+def decoder_layer_forced(cfg, w: dict, i: int, h: torch.Tensor, positions: torch.Tensor, operands):
+    """``decoder_layer`` with every GEMM fed the quantised operands a device run used (see ``vision_block_forced``).
+    Returns (next hidden states, the oracle's own tensors at the four quantisation points)."""
+    S, D = cfg.tokens, cfg.head_dim
+    l = f"model.layers.{i}"
+    refs = [ops.rmsnorm(h, w[f"{l}.input_layernorm.weight"], cfg.eps)]
+    q = _fp8_linear(w, f"{l}.self_attn.q_proj", *operands[0]).view(S, cfg.heads, D)
+    k = _fp8_linear(w, f"{l}.self_attn.k_proj", *operands[0]).view(S, cfg.kv_heads, D)
+    v = _fp8_linear(w, f"{l}.self_attn.v_proj", *operands[0]).view(S, cfg.kv_heads, D)
+    q, k = ops.mrope(q, positions, cfg.theta, cfg.sections), ops.mrope(k, positions, cfg.theta, cfg.sections)
+    refs.append(ops.attention(q, k, v, mask="causal").reshape(S, cfg.q_dim))
+    h2 = _fp8_linear(w, f"{l}.self_attn.o_proj", *operands[1], residual=h)
+    refs.append(ops.rmsnorm(h2, w[f"{l}.post_attention_layernorm.weight"], cfg.eps))
+    refs.append(ops.swiglu(_fp8_linear(w, f"{l}.mlp.gate_proj", *operands[2]), _fp8_linear(w, f"{l}.mlp.up_proj", *operands[2])))
+    return _fp8_linear(w, f"{l}.mlp.down_proj", *operands[3], residual=h2), refs
 
 
 def language_model(cfg, w: dict, h: torch.Tensor, positions: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
