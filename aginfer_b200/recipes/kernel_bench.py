@@ -25,7 +25,8 @@ GEMM_SHAPES = {"gemm_q": (D, D), "gemm_fc1": (MLP, D), "gemm_fc2": (D, MLP),
                "gemm_1024x1024": (1024, 1024), "gemm_512x1024": (512, 1024), "gemm_4096x1024": (4096, 1024),
                "gemm_1024x4096": (1024, 4096),     # action expert
                "gemm_3584x3584": (3584, 3584), "gemm_18944x3584": (18944, 3584), "gemm_3584x18944": (3584, 18944)}
-CASES = ("empty", "layernorm", "attn_self", "attn_cross", "attn_prefill", "attn_vision", *GEMM_SHAPES)
+CASES = ("empty", "layernorm", "attn_self", "attn_cross", "attn_prefill", "attn_vision", "group_qkv", "batch_kv",
+         "quantize_packed", "rmsnorm_amax", "mrope", "swiglu_amax", "dit_blocks", *GEMM_SHAPES)
 
 
 def build(case: str, tactic: str, reps: int, tokens: int, stages: int = 4, dtype: str = "bf16", packed: bool = False):
@@ -46,6 +47,20 @@ def build(case: str, tactic: str, reps: int, tokens: int, stages: int = 4, dtype
                 from .layout import pack_kblock_swizzled
                 weights[f"l{l}.w"] = pack_kblock_swizzled(weights[f"l{l}.w"])
         weights["w_scale"] = torch.tensor(0.08 / 448, dtype=torch.float32)
+    if case == "group_qkv":       # decoder Q | K | V (2048 | 256 | 256 rows, K = 2048) as one grouped tensor-core launch
+        from .layout import pack_kblock_swizzled
+        g = torch.Generator().manual_seed(0)
+        for l in range(LAYERS):
+            for part, n in (("q", 2048), ("k", 256), ("v", 256)):
+                w = (torch.randn(n, 2048, generator=g) * 0.02).clamp(-0.08, 0.08).mul(448 / 0.08).to(torch.float8_e4m3fn)
+                weights[f"l{l}.{part}"] = pack_kblock_swizzled(w) if packed else w
+        weights["w_scale"] = torch.tensor(0.08 / 448, dtype=torch.float32)
+    if case == "batch_kv":        # the action head's cross-attention K / V projections: 16 x (1536 x 2048) bf16, one launch
+        g = torch.Generator().manual_seed(0)
+        for l in range(LAYERS):
+            weights[f"l{l}.w"] = (torch.randn(D, 2048, generator=g) * 0.02).to(torch.bfloat16)
+    if case in ("rmsnorm_amax",):
+        weights["gain"] = torch.ones(2048, dtype=torch.bfloat16)
     r = RecipeBuilder(describe(weights))
     r.begin_profile("default", [io("token", "I32", [1])], [io("status", "I32", [1])])
     big = (max(tokens, 64) + 512) * 18944 * 2     # room for the padded rows of packed activations
@@ -64,6 +79,23 @@ def build(case: str, tactic: str, reps: int, tokens: int, stages: int = 4, dtype
         elif case == "attn_prefill":      # decoder prefill: `tokens` causal rows, 16 query / 2 KV heads of 128
             r.attention(q, kbuf, vbuf, y, q_rows=tokens, kv_rows=tokens, q_heads=16, kv_heads=2, head_dim=128,
                         q_stride=2048, k_stride=256, v_stride=256, o_stride=2048, mask="causal")
+        elif case == "group_qkv":
+            dummy_bias = None
+            r.gemm_group(x, [(Weight(f"l{i % LAYERS}.q"), dummy_bias, Weight("w_scale"), y, 2048, 2560),
+                             (Weight(f"l{i % LAYERS}.k"), dummy_bias, Weight("w_scale"), y + 2048 * 2, 256, 2560),
+                             (Weight(f"l{i % LAYERS}.v"), dummy_bias, Weight("w_scale"), y + 2304 * 2, 256, 2560)],
+                         tokens, 2048, dtype="e4m3", scale_a=scale_a, packed=packed)
+        elif case == "batch_kv":
+            r.gemm_batch(x, [(Weight(f"l{j}.w"), Weight("bias")) for j in range(LAYERS)], y, tokens, D, 2048,
+                         seg_stride=tokens * D)
+        elif case == "quantize_packed":   # amax is taken as already folded by the producer (one launch)
+            r.quantize_e4m3(x, y, scale_a, tokens * 2048, amax=r.counter() if i == 0 else Arena(64), packed=(tokens, 2048))
+        elif case == "rmsnorm_amax":
+            r.rmsnorm(x, Weight("gain"), y, tokens, 2048, 1e-6, amax=Arena(64))
+        elif case == "mrope":
+            r.mrope(x, kbuf, tokens, 16, 128, 2048, 1e6, (16, 24, 24))
+        elif case == "swiglu_amax":
+            r.swiglu(x, x + 11008 * 2, y, tokens, 11008, 2 * 11008, amax=Arena(64))
         elif case == "attn_vision":       # vision tower: `tokens` patch rows, 16 heads of 80, 64-token windows
             r.attention(q, kbuf, vbuf, y, q_rows=tokens, kv_rows=tokens, q_heads=16, kv_heads=16, head_dim=80,
                         q_stride=1280, k_stride=1280, v_stride=1280, o_stride=1280, mask="block", mask_arg=64)
@@ -95,12 +127,23 @@ def main() -> None:
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "e4m3"])
     ap.add_argument("--packed", action="store_true", help="e4m3 only: packed operands, bulk-copy producers")
     ap.add_argument("--stages", type=int, default=4, help="K partitions of the bulk-stream GEMM (1-4)")
+    ap.add_argument("--layers", type=int, default=2, help="blocks in the stack of the dit_blocks case")
     args = ap.parse_args()
 
-    weights, recipe = build(args.case, args.tactic, args.reps, args.tokens, args.stages, args.dtype, args.packed)
+    profile = ""
+    if args.case == "dit_blocks":
+        # the persistent block kernel over `--layers` blocks of the action head's shape: the recipe's own
+        # measurement profile (pointer table + one launch); --reps does not apply
+        from . import dit
+        cfg = dit.DitConfig(layers=args.layers)
+        weights = dit.synthetic_weights(cfg, seed=2)
+        recipe = dit.build_recipe(cfg, stream_profile=True, block_kernel=True)
+        profile, args.reps = "blocks_1", 1
+    else:
+        weights, recipe = build(args.case, args.tactic, args.reps, args.tokens, args.stages, args.dtype, args.packed)
     with tempfile.TemporaryDirectory() as tmp:
         aim = build_aim(Path(tmp), weights, recipe)
-        runner = Runner(aim, flags=rt.PROGRAMMATIC_LAUNCH if args.pdl else 0)
+        runner = Runner(aim, profile=profile, flags=rt.PROGRAMMATIC_LAUNCH if args.pdl else 0)
         token = torch.zeros(1, dtype=torch.int32, device="cuda")
         status = torch.zeros(1, dtype=torch.int32, device="cuda")
         stream = torch.cuda.Stream()
@@ -114,6 +157,13 @@ def main() -> None:
                 runner.run({"token": token}, {"status": status}, stream=stream)
             end.record(stream)
             torch.cuda.synchronize()
+        if args.case == "dit_blocks":
+            from . import dit
+            alg, _ = dit.stream_profile_bytes(cfg)
+            ms = start.elapsed_time(end) / args.iters
+            print(f"dit_blocks layers={args.layers}: {ms * 1000:.1f} us per profile replay (pointer table + one launch), "
+                  f"{alg / ms / 1e6:.0f} GB/s of algorithmic bytes, status={status.item()}")
+            return
         us = start.elapsed_time(end) * 1000.0 / args.iters / (args.reps + 2)
         line = f"{args.case} tactic={args.tactic} tokens={args.tokens} pdl={args.pdl} packed={args.packed}: {us:.2f} us/launch"
         if args.case in GEMM_SHAPES:
