@@ -109,7 +109,8 @@ def test_fp8_blocks_hold_the_tight_tier_when_the_operands_are_teacher_forced(tmp
     rounding (held to 2e-2, the tier of GEMM and block outputs).  What sits between two GEMMs (norm, rotary
     embedding, attention, SwiGLU, quantiser) is checked through the operands themselves: each exported operand,
     dequantised, against the oracle's own tensor at that point, within the E4M3 grid's resolution (half a step of
-    the top binade = 16 / 448 of the range), and its scale against amax / 448 of the same tensor."""
+    the top binade = 16 / 448 of the range) plus the 1e-2 that kernels fed identical inputs are held to, and its
+    scale against amax / 448 of the same tensor."""
     cfg = qwen_vl.VlConfig(**REDUCED)
     blocks = ("visual.blocks.0", "visual.blocks.3", "model.layers.0", "model.layers.3")
     w, x = qwen_vl.synthetic_weights(cfg), qwen_vl.synthetic_inputs(cfg)
@@ -131,6 +132,6 @@ def test_fp8_blocks_hold_the_tight_tier_when_the_operands_are_teacher_forced(tmp
         scales = [abs(float(s) / (float(ref.float().abs().max()) / 448.0) - 1.0) for (q, s), ref in zip(operands, refs)]
         report[block] = (round(err, 5), [round(g, 4) for g in grid], [round(v, 5) for v in scales])
         assert err <= 2e-2, (block, err)
-        assert max(grid) <= 16.0 / 448.0 + 1e-3, (block, grid)
+        assert max(grid) <= 16.0 / 448.0 + 1e-2, (block, grid)      # half a top-binade step + the kernels' own 1e-2
         assert max(scales) <= 1e-2, (block, scales)
     print("operand-teacher-forced blocks (output error, operand error per quantisation point, scale deviation):", report)
