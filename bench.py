@@ -205,12 +205,17 @@ def bench_action_head(args, group, harness, session_flags) -> tuple[dict, dict]:
     stream = harness.stream
     dev_in = {k: v.cuda() for k, v in inputs.items()}
     out = runner.empty_outputs()
-    warmup = max(args.warmup, 3)
+    warmup = max(args.warmup, 3) if args.legs != "device" else args.warmup
 
     # ---- device-resident leg: inputs already in HBM; exactly --steps chunks between the barriers ----
     chunk = lambda: runner.run(dev_in, out, stream=stream)
     harness.warm(chunk, warmup)
     ms = harness.timed(chunk, args.steps)
+    if args.legs == "device":      # small profiler captures: nothing but the device-resident leg
+        ms, = group.max_over_ranks([ms])
+        line = {"metric": METRIC, "value": group.whole_job_rate(args.steps, ms), "unit": UNIT, "n_gpus": group.world,
+                "steps": args.steps, "ms_per_step": ms / args.steps}
+        return line, {"tmp": tmp}
     spread = [harness.timed(chunk, args.steps) / args.steps for _ in range(SPREAD_REPEATS)]
 
     # ---- end-to-end leg: pinned host inputs in, actions out, every chunk ----
@@ -236,6 +241,40 @@ def bench_action_head(args, group, harness, session_flags) -> tuple[dict, dict]:
     plain_steps = max(3, min(args.steps, 50))
     ms_plain = harness.timed(plain_chunk, plain_steps) / plain_steps
     del plain
+
+    # ---- two and three independent sessions of the same package on one GPU, each on its own stream ----
+    # (an extra figure, not the headline: a chunk's latency stays what it is, but a GPU that one batch-1 episode
+    #  keeps at a fifth of its HBM bandwidth can serve several episodes at once)
+    concurrent = {}
+    for sessions in (2, 3):
+        lanes = []
+        for _ in range(sessions):
+            lane_stream = torch.cuda.Stream()
+            lane_runner = Runner(aim, profile="default", flags=session_flags)
+            lane_in, lane_out = {k: v.clone() for k, v in dev_in.items()}, lane_runner.empty_outputs()
+            lanes.append((lane_runner, lane_stream, lane_in, lane_out))
+
+        def all_lanes():
+            for lane_runner, lane_stream, lane_in, lane_out in lanes:
+                lane_runner.run(lane_in, lane_out, stream=lane_stream)
+
+        for _ in range(3):
+            all_lanes()
+        torch.cuda.synchronize()
+        marks = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in lanes]
+        harness.barrier()
+        first = torch.cuda.Event(enable_timing=True)
+        first.record(lanes[0][1])
+        rounds = max(10, args.steps // 4)
+        for _ in range(rounds):
+            all_lanes()
+        for (_, lane_stream, _, _), (_, done) in zip(lanes, marks):
+            done.record(lane_stream)
+        harness.barrier()
+        lane_ms = max(first.elapsed_time(done) for _, done in marks)
+        concurrent[f"{sessions}_sessions"] = {"chunks_per_s": sessions * rounds / (lane_ms / 1e3) * group.world,
+                                              "ms_per_round": lane_ms / rounds}
+        del lanes
 
     # ---- after the timed regions: the chunk that was timed is the right one ----
     chunk()
@@ -269,6 +308,8 @@ def bench_action_head(args, group, harness, session_flags) -> tuple[dict, dict]:
         "gpu_launches": int(stats["launches_per_enqueue"]) * args.steps,
         "launches_per_chunk": int(stats["launches_per_enqueue"]),
         "check": {"status_word": status_word, "cosine_vs_cpu_oracle": cosine},
+        "concurrent_sessions_per_gpu": {**concurrent, "how": "independent sessions of the same package on separate streams "
+                                        "of one GPU, device-resident inputs; this rank's figure times the number of ranks"},
     }
     context = {"aim": aim, "cfg": cfg, "weights": weights, "inputs": inputs, "tmp": tmp, "per_chunk_bytes": acc["per_chunk"]}
     return line, context

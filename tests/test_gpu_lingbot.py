@@ -79,4 +79,4 @@ def test_full_depth_episode_matches_oracle(tmp_path):
     print(f"full-depth episode: actions given the same cache cosine={cos:.6f} max_rel_err={err:.3e}; free-running "
           f"actions cosine={free_cos:.5f}, K/V cache cosine={cache_cos:.5f}; launches={runner.stats()['launches_per_enqueue']}")
     assert cos >= 0.999 and err < 2e-2
-    assert cache_cos >= 0.95 and free_cos >= 0.95
+    assert cache_cos >= 0.95 and free_cos >= 0.995      # measured: 0.9823 and 0.9996
