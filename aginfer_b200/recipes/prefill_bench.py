@@ -39,6 +39,9 @@ def main() -> None:
     ap.add_argument("--tactic", default="auto")
     ap.add_argument("--packed", action="store_true", help="packed weights / activations, bulk-copy GEMM producers")
     ap.add_argument("--save-outputs", default=None, help="write hidden_out / kv_cache / status as a .pt file")
+    ap.add_argument("--load-timing", action="store_true",
+                    help="also time the package load (integrity hashing) and the weight upload, pinned double-buffered "
+                         "against one blocking copy from the file mapping")
     args = ap.parse_args()
     full = tuple(i for i in (7, 15, 23, 31) if i < args.v_layers) or (args.v_layers - 1,)
     t0 = time.time()
@@ -64,6 +67,18 @@ def main() -> None:
     tmp = Path(tempfile.mkdtemp(prefix="agi_prefill_", dir=scratch))
     try:
         aim = build_aim(tmp, weights, recipe)
+        load_timing = None
+        if args.load_timing:
+            load_timing = {"aim_bytes": aim.stat().st_size}
+            a = time.time()
+            rt.Model.load(aim)                               # mmap + whole-file and per-section SHA-256
+            load_timing["model_load_seconds"] = time.time() - a
+            for label, flag in (("pinned_double_buffered", 0), ("blocking_from_mapping", rt.BLOCKING_UPLOAD)):
+                probe = Runner(aim, flags=flag | rt.NO_GRAPH_REPLAY)
+                probe.run({k: v.cuda() for k, v in inputs.items()}, probe.empty_outputs())
+                torch.cuda.synchronize()
+                load_timing[f"upload_seconds_{label}"] = probe.stats()["upload_seconds"]
+                del probe
         t1 = time.time()
         runner = Runner(aim, flags=rt.PROGRAMMATIC_LAUNCH if args.pdl else 0)
         stream = torch.cuda.Stream()
@@ -95,6 +110,7 @@ def main() -> None:
             "fp8_weight_gb": alg["fp8_weight_bytes"] / 1e9, "weight_stream_gbs": alg["fp8_weight_bytes"] / ms / 1e6,
             "tflops": alg["flops"] / ms / 1e9, "status": int(out["status"].item()),
             "setup_s": {"weights_and_package": t1 - t0, "load_and_first_runs": time.time() - t1 - ms * args.iters / 1e3},
+            **({"load_timing": load_timing} if load_timing else {}),
         }))
         if args.save_outputs:
             torch.save({k: v.cpu() for k, v in out.items()}, args.save_outputs)
