@@ -204,6 +204,48 @@ def tc_cluster_tiling(M: int, N: int, K: int, elem: int, dtype: str = "bf16") ->
             "shared_bytes": stages * stage_bytes + 1024 + gather_bytes}
 
 
+TCS_CLUSTER_SIZES = (2, 3, 4, 6, 8)       # compiled cluster variants of agi_gemm_tcs_bf16
+TCS_MAX_BLOCKS = 8                        # K blocks of 64 elements per slice: the slab a CTA requests at once (128 KB)
+TCS_TARGET_CTAS = 2 * SM_COUNT            # two CTAs per SM keep the SM's copy engine busy while one of them computes
+
+
+def tcs_tiling(M: int, tiles: int, K: int, cluster: int | None = None, groups: int | None = None,
+               kb: int | None = None) -> dict[str, int] | None:
+    """Geometry of ``agi_gemm_tcs_bf16[_c{C}]`` (packed bf16 weights, at most 32 tokens): K is cut into
+    ``cluster * groups`` slices of ``kb`` blocks of 64 elements; the slices of a cluster meet in distributed shared
+    memory, the ``groups`` clusters of a tile (or, with cluster 1, all slices) in global fp32 slabs.
+
+    Chosen: the most slices that keep the grid within two CTAs per SM with at least two K blocks each; one
+    cluster per tile when eight slices of at most TCS_MAX_BLOCKS cover K, several clusters otherwise."""
+    if M > 32 or K % 64:
+        return None
+    k_blocks = K // 64
+    if cluster is None or groups is None or kb is None:
+        options = [s for s in range(1, 33) if k_blocks % s == 0 and 2 <= k_blocks // s <= TCS_MAX_BLOCKS
+                   and tiles * s <= TCS_TARGET_CTAS]
+        if not options:
+            options = [s for s in range(1, 33) if k_blocks % s == 0 and k_blocks // s <= TCS_MAX_BLOCKS][:1]
+        if not options:
+            return None
+        slices = max(options)
+        if slices > 8 and k_blocks % 8 == 0 and k_blocks // 8 <= TCS_MAX_BLOCKS:
+            slices = 8
+        if slices in (1, *TCS_CLUSTER_SIZES):
+            cluster, groups = slices, 1
+        else:
+            cluster = max((c for c in TCS_CLUSTER_SIZES if slices % c == 0 and slices // c <= 4), default=None)
+            if cluster is None:
+                return None
+            groups = slices // cluster
+        kb = k_blocks // slices
+    slices = cluster * groups
+    assert slices * kb >= k_blocks and kb <= TCS_MAX_BLOCKS and (cluster == 1 or cluster in TCS_CLUSTER_SIZES)
+    assert slices <= 16 if cluster == 1 else groups <= 4
+    gather = cluster * ceil_div(32, cluster) * 512 if cluster > 1 else 0
+    return {"cluster": cluster, "groups": groups, "kb": kb, "slices": slices, "ctas": tiles * slices,
+            "shared_bytes": kb * 20480 + 1024 + gather}
+
+
 def stream_tiling(M: int, N: int, K: int, elem: int, extra_rows: int = 0, contiguous: bool = True) -> dict[str, int]:
     """Launch geometry of ``agi_gemm_stream_*``: rows per CTA, K windows per ring slot, slots.
 
@@ -498,6 +540,10 @@ class RecipeBuilder:
         """Y[M, N] = epilogue(X[M, K] . W[N, K]^T); ``dtype`` names the operand type (bf16 or e4m3).
         ``packed`` (E4M3 only): both operands are in the packed layout of ``recipes/layout.py`` (weights packed
         at packaging time, activations by ``quantize_e4m3(..., packed=)``) and ring slots are filled by bulk copies."""
+        if dtype == "bf16" and self.is_packed(w):
+            assert not out_f32 and scale_a is None, "the packed bf16 GEMM writes bf16 and takes no scales"
+            self.gemm_tcs(x, [(w, bias, N)], y, M, K, residual=residual, act=act, ldx=ldx, ldy=ldy)
+            return
         if packed:
             assert dtype == "e4m3" and K % 128 == 0 and ldx is None
             t = tc_prefill_plan(M, N, K, 1)
@@ -677,6 +723,39 @@ class RecipeBuilder:
                      U32(t["stages"]), U32(seg_stride), *ws, *bs], shared_bytes=t["shared_bytes"], op="gemm_bf16_batch",
                     algorithm=f"tcgen05_128x{t['TN']}_s{t['stages']}_x{len(parts)}")
 
+    def is_packed(self, w: Pointer) -> bool:
+        """True for a checkpoint matrix stored in the packed layout of ``recipes/layout.py`` ([K blocks, rows, 64])."""
+        return isinstance(w, Weight) and len(self.weights.get(w.name, ("", ()))[1]) == 3
+
+    def gemm_tcs(self, x: Pointer, parts: Sequence[tuple[Pointer, Pointer | None, int]], y: Pointer, M: int, K: int, *,
+                 residual: Pointer | None = None, act: str | None = None, ldx: int | None = None,
+                 ldy: int | None = None, cluster: int | None = None, groups: int | None = None,
+                 kb: int | None = None) -> None:
+        """``y[:, blocks] = epilogue(x . [W0 | W1 | W2]^T)`` with packed bf16 weights and M <= 32: the
+        weight-streaming tensor-core kernel (every CTA requests its whole weight slab before the grid-dependency
+        wait).  ``parts``: up to three ``(packed weight, bias or None, N_i)``, N_i multiples of 128."""
+        assert 1 <= len(parts) <= 3 and all(n % 128 == 0 for _, _, n in parts)
+        assert len({b is None for _, b, _ in parts}) == 1 and ((ldx or K) * 2) % 16 == 0
+        total = sum(n for _, _, n in parts)
+        t = tcs_tiling(M, total // 128, K, cluster, groups, kb)
+        if t is None:
+            raise ValueError("the weight-streaming tensor-core GEMM needs M <= 32 and K in whole 64-element blocks")
+        partial, counters = self._tc_scratch
+        assert t["slices"] * M * total * 4 <= TC_SCRATCH_BYTES and total // 128 * 8 * 4 <= TC_COUNTER_BYTES
+        flags = ACT[act] | (FLAG_BIAS if parts[0][1] is not None else 0) | (FLAG_RESIDUAL if residual else 0)
+        dummy = Arena(0)
+        ws = [p[0] for p in parts] + [dummy] * (3 - len(parts))
+        bs = [(p[1] or dummy) for p in parts] + [dummy] * (3 - len(parts))
+        ns = [p[2] for p in parts] + [0] * (3 - len(parts))
+        C, G = t["cluster"], t["groups"]
+        kernel = "agi_gemm_tcs_bf16" if C == 1 else f"agi_gemm_tcs_bf16_c{C}"
+        grid = (total // 128, 1, t["slices"]) if C == 1 else (total // 128, G, C)
+        self.launch(kernel, grid, (160, 1, 1),
+                    [x, *ws, y, *bs, residual or dummy, partial, counters, Arena(STATUS_WORD), U32(M), *map(U32, ns),
+                     U32(K), U32(ldx or K), U32(ldy or total), U32(flags), U32(t["kb"])],
+                    shared_bytes=t["shared_bytes"], op="gemm_bf16_packed",
+                    algorithm=f"tcgen05_stream_kb{t['kb']}_c{C}_g{G}_x{len(parts)}")
+
     def fused_linear(self, x: Pointer, parts: Sequence[tuple[Pointer, Pointer | None, int]], y: Pointer, M: int, K: int,
                      *, ln: dict[str, Any] | None = None, ln_scratch: Pointer | None = None,
                      residual: Pointer | None = None, act: str | None = None, ldx: int | None = None,
@@ -692,6 +771,14 @@ class RecipeBuilder:
         one launch per weight matrix."""
         total = sum(n for _, _, n in parts)
         ldy = ldy or total
+        if all(self.is_packed(w) for w, _, _ in parts):
+            src = x
+            if ln is not None:
+                assert ln_scratch is not None, "a separate LayerNorm needs a buffer for the normalised activations"
+                self.layernorm(x, ln_scratch, M, K, ln["eps"], scale=ln.get("scale"), shift=ln.get("shift"), x_stride=ldx)
+                src, ldx = ln_scratch, None
+            self.gemm_tcs(src, parts, y, M, K, residual=residual, act=act, ldx=ldx, ldy=ldy)
+            return
         t = stream_tiling(M, total, K, 2, contiguous=(ldx or K) == K)
         rows = t["rows"]
         fits = (M <= 64 and (K * 2) % 64 == 0 and len(parts) <= 3 and all(n % rows == 0 for _, _, n in parts)

@@ -101,6 +101,29 @@ def synthetic_weights(cfg: DitConfig, seed: int = 2, std: float = 0.02) -> dict:
             for name, shape in sorted(weight_shapes(cfg).items())}
 
 
+def packed_names(cfg: DitConfig) -> list[str]:
+    """The block matrices that are multiplied with the 17-token sequence once per denoising step: queries (and keys,
+    values of the self-attention blocks), attention output, MLP up and down.  The cross-attention key / value
+    projections run once per chunk over the context tokens and stay row-major."""
+    names = []
+    for l in range(cfg.layers):
+        b = f"{P}.dit.blocks.{l}"
+        names += [f"{b}.attn.to_q.weight", f"{b}.attn.to_out.weight", f"{b}.ff.fc1.weight", f"{b}.ff.fc2.weight"]
+        if not cfg.is_cross(l):
+            names += [f"{b}.attn.to_k.weight", f"{b}.attn.to_v.weight"]
+    return names
+
+
+def pack_checkpoint(cfg: DitConfig, weights: dict) -> dict:
+    """Packaging-time layout pass: the matrices of ``packed_names`` are replaced (same name) by their packed form
+    [K / 64, N, 64] for the weight-streaming tensor-core GEMM (see ``layout.py``).  Values are untouched, so the
+    oracle keeps using the row-major checkpoint.  Needs hidden and MLP widths in whole 128-row tiles."""
+    from .layout import pack_kblock_swizzled
+    chosen = set(packed_names(cfg))
+    return {k: pack_kblock_swizzled(v) if k in chosen and v.dim() == 2 and v.shape[0] % 128 == 0 and v.shape[1] % 64 == 0
+            else v for k, v in weights.items()}
+
+
 def synthetic_inputs(cfg: DitConfig, seed: int = 2) -> dict:
     """Backbone tokens, state and initial noise ~ N(0, 1), BF16 (noise is an explicit input: the
     loader ignores RunOptions.seed just as the reference does)."""
@@ -128,6 +151,8 @@ def build_recipe(cfg: DitConfig = DitConfig(), weights: Mapping[str, tuple[str, 
     if block_kernel and not fits:
         raise ValueError("this shape is outside what the persistent block kernel covers")
     r = RecipeBuilder(weights or {k: ("BF16", v) for k, v in weight_shapes(cfg).items()})
+    if block_kernel and any(r.is_packed(Weight(n)) for n in packed_names(cfg)):
+        raise ValueError("the persistent block kernel reads row-major weights; package the checkpoint unpacked")
     if block_kernel:
         r.dit_scratch(T, D, cfg.mlp)      # outlives every profile: allocated before the first mark
     variants = [(profile, cfg.steps)] + [(f"{profile}/steps={n}", n) for n in step_profiles]

@@ -29,7 +29,8 @@ CASES = ("empty", "layernorm", "attn_self", "attn_cross", "attn_prefill", "attn_
          "quantize_packed", "rmsnorm_amax", "mrope", "swiglu_amax", "dit_blocks", *GEMM_SHAPES)
 
 
-def build(case: str, tactic: str, reps: int, tokens: int, stages: int = 4, dtype: str = "bf16", packed: bool = False):
+def build(case: str, tactic: str, reps: int, tokens: int, stages: int = 4, dtype: str = "bf16", packed: bool = False,
+          tcs: tuple[int, int, int] | None = None):
     import torch
 
     from . import Arena, RecipeBuilder, Tensor, U32, Weight, io
@@ -101,7 +102,10 @@ def build(case: str, tactic: str, reps: int, tokens: int, stages: int = 4, dtype
                         q_stride=1280, k_stride=1280, v_stride=1280, o_stride=1280, mask="block", mask_arg=64)
         else:
             n, k = GEMM_SHAPES[case]
-            if dtype == "bf16":
+            if dtype == "bf16" and packed:    # weight-streaming tensor-core kernel; geometry from --tcs or the builder
+                c, g, kb = tcs or (None, None, None)
+                r.gemm_tcs(x, [(Weight(f"l{i % LAYERS}.w"), None, n)], y, tokens, k, cluster=c, groups=g, kb=kb)
+            elif dtype == "bf16":
                 r.gemm(x, Weight(f"l{i % LAYERS}.w"), y, tokens, n, k, tactic=tactic)
             else:   # activations taken as already quantised bytes; scales are whatever the arena holds
                 r.gemm(x, Weight(f"l{i % LAYERS}.w"), y, tokens, n, k, dtype="e4m3", scale_a=scale_a,
@@ -125,7 +129,9 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=T)
     ap.add_argument("--pdl", action="store_true")
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "e4m3"])
-    ap.add_argument("--packed", action="store_true", help="e4m3 only: packed operands, bulk-copy producers")
+    ap.add_argument("--packed", action="store_true", help="packed weights (and, for e4m3, activations), bulk-copy producers")
+    ap.add_argument("--tcs", default=None, help="packed bf16 only: cluster,groups,blocks-per-slice of the weight-streaming "
+                                                "tensor-core kernel (default: the builder's choice)")
     ap.add_argument("--stages", type=int, default=4, help="K partitions of the bulk-stream GEMM (1-4)")
     ap.add_argument("--layers", type=int, default=2, help="blocks in the stack of the dit_blocks case")
     args = ap.parse_args()
@@ -140,7 +146,8 @@ def main() -> None:
         recipe = dit.build_recipe(cfg, stream_profile=True, block_kernel=True)
         profile, args.reps = "blocks_1", 1
     else:
-        weights, recipe = build(args.case, args.tactic, args.reps, args.tokens, args.stages, args.dtype, args.packed)
+        weights, recipe = build(args.case, args.tactic, args.reps, args.tokens, args.stages, args.dtype, args.packed,
+                                tuple(map(int, args.tcs.split(","))) if args.tcs else None)
     with tempfile.TemporaryDirectory() as tmp:
         aim = build_aim(Path(tmp), weights, recipe)
         runner = Runner(aim, profile=profile, flags=rt.PROGRAMMATIC_LAUNCH if args.pdl else 0)
@@ -165,7 +172,8 @@ def main() -> None:
                   f"{alg / ms / 1e6:.0f} GB/s of algorithmic bytes, status={status.item()}")
             return
         us = start.elapsed_time(end) * 1000.0 / args.iters / (args.reps + 2)
-        line = f"{args.case} tactic={args.tactic} tokens={args.tokens} pdl={args.pdl} packed={args.packed}: {us:.2f} us/launch"
+        line = (f"{args.case} tactic={args.tactic} tokens={args.tokens} pdl={args.pdl} packed={args.packed}"
+                + (f" tcs={args.tcs}" if args.tcs else "") + f": {us:.2f} us/launch")
         if args.case in GEMM_SHAPES:
             n, k = GEMM_SHAPES[args.case]
             elem = 2 if args.dtype == "bf16" else 1

@@ -77,3 +77,33 @@ def test_oracle_runs_and_is_deterministic_on_a_tiny_shape():
     assert a.shape == (16, 32) and a.dtype == torch.float32 and torch.equal(a, b)
     assert torch.isfinite(a).all() and not torch.equal(a, x["noise"].float())
     assert dit.build_recipe(TINY).plan()["arena_bytes"] > 0
+
+
+def test_packed_checkpoint_routes_the_block_matrices_to_the_tensor_core_stream_kernel():
+    """The packaging-time layout pass keeps names and values (it is undone exactly) and the recipe, given the packed
+    shapes, multiplies those matrices with agi_gemm_tcs_bf16*; the cross-attention K / V projections stay row-major."""
+    import collections
+
+    import torch
+
+    from aginfer_b200.recipes.builder import tcs_tiling
+    from aginfer_b200.recipes.layout import unpack_kblock_swizzled
+    from aginfer_b200.recipes.package import describe
+    cfg = dit.DitConfig(layers=2)
+    w = dit.synthetic_weights(cfg, seed=2)
+    packed = dit.pack_checkpoint(cfg, w)
+    names = dit.packed_names(cfg)
+    assert len(names) == 4 + 6 and all(packed[n].dim() == 3 for n in names)
+    assert all(torch.equal(unpack_kblock_swizzled(packed[n], w[n].shape[0]), w[n]) for n in names)
+    assert all(packed[k] is v for k, v in w.items() if k not in names)
+    recipe = dit.build_recipe(cfg, describe(packed))
+    kernels = collections.Counter(l["kernel"] for l in recipe.plan()["shape_dispatch"][0]["launches"])
+    tcs = {k: v for k, v in kernels.items() if k.startswith("agi_gemm_tcs_bf16")}
+    assert sum(tcs.values()) == cfg.steps * cfg.layers * 4 and kernels["agi_gemm_tc_bf16_x16"] >= 1
+    with pytest.raises(ValueError, match="row-major"):
+        dit.build_recipe(cfg, describe(packed), block_kernel=True)
+    # the geometry chosen for the head's four shapes: at most two CTAs per SM, K slices of 3-4 blocks
+    for tiles, K, want in ((48, 1536, (6, 1, 4)), (36, 1536, (8, 1, 3)), (12, 1536, (8, 1, 3)), (12, 6144, (8, 3, 4))):
+        t = tcs_tiling(17, tiles, K)
+        assert (t["cluster"], t["groups"], t["kb"]) == want and t["ctas"] <= 296 and t["shared_bytes"] <= 113 * 1024
+    assert tcs_tiling(33, 12, 1536) is None and tcs_tiling(17, 12, 1000) is None

@@ -15,8 +15,13 @@ from tests.test_dit_cpu import TINY
 pytestmark = pytest.mark.gpu
 
 
-def run_chunk(tmp_path, cfg, weights, inputs, gemm_tactic="auto", repeats=2, block_kernel=None, flags=0):
-    recipe = dit.build_recipe(cfg, gemm_tactic=gemm_tactic, block_kernel=block_kernel)
+def run_chunk(tmp_path, cfg, weights, inputs, gemm_tactic="auto", repeats=2, block_kernel=None, flags=0, packed=False):
+    inventory = None
+    if packed:      # the packaging-time layout pass; the recipe sees the packed shapes and picks the kernels for them
+        from aginfer_b200.recipes.package import describe
+        weights = dit.pack_checkpoint(cfg, weights)
+        inventory = describe(weights)
+    recipe = dit.build_recipe(cfg, inventory, gemm_tactic=gemm_tactic, block_kernel=block_kernel)
     aim = build_aim(tmp_path, weights, recipe, steps=cfg.steps, action_horizon=cfg.horizon, state_length=cfg.state_dim)
     runner = Runner(aim, flags=flags)
     dev = {k: v.cuda() for k, v in inputs.items()}
@@ -47,15 +52,16 @@ def test_tiny_dit_block_kernel_launch_modes(tmp_path, flags):
     assert torch.equal(got, base)
 
 
-@pytest.mark.parametrize("block_kernel", [False, True])
-def test_full_size_action_chunk_matches_oracle(tmp_path, block_kernel):
+@pytest.mark.parametrize("block_kernel,packed", [(False, False), (True, False), (False, True)],
+                         ids=["launch_per_op", "block_kernel", "packed_weights"])
+def test_full_size_action_chunk_matches_oracle(tmp_path, block_kernel, packed):
     # BASELINE config 3: 16 blocks x 1536, 17 tokens, 300 backbone tokens, 4 Euler steps, seed 2
     cfg = dit.DitConfig()
     w, x = dit.synthetic_weights(cfg, seed=2), dit.synthetic_inputs(cfg, seed=2)
-    got, stats = run_chunk(tmp_path, cfg, w, x, block_kernel=block_kernel)
+    got, stats = run_chunk(tmp_path, cfg, w, x, block_kernel=block_kernel, packed=packed)
     want = oracle_dit.forward(cfg, w, x["backbone_features"], x["state"], x["noise"])
     cos, err = ops.cosine(got, want), ops.max_rel_err(got, want)
-    print(f"full DiT (block kernel {block_kernel}): cosine={cos:.6f} max_rel_err={err:.3e} "
+    print(f"full DiT (block kernel {block_kernel}, packed {packed}): cosine={cos:.6f} max_rel_err={err:.3e} "
           f"launches/chunk={stats['launches_per_enqueue']}")
     assert cos >= 0.999 and err < 2e-2
     # a fresh session reproduces the chunk bit for bit: partial sums are added in a fixed order

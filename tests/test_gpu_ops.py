@@ -628,3 +628,44 @@ def test_gemm_tcgen05_cluster_split_k(tmp_path, case):
     got, _ = run_recipe(tmp_path, weights, inputs, {"y": (BF, (M, N)), "status": (torch.int32, (1,))}, body, repeats=3)
     assert got["status"].item() == 0, hex(got["status"].item())
     assert ops.max_rel_err(got["y"], ops.gemm(x, w, bias=bias, residual=res, act=act)) < 1e-2
+
+
+# (M, widths, K, epilogue, cluster, groups, K blocks per slice); None = the builder's own choice
+TCS_CASES = [(17, (1536,), 1536, "bias_gelu_res", None, None, None), (17, (6144,), 1536, "bias_gelu", None, None, None),
+             (17, (1536,), 6144, "bias_res", None, None, None), (17, (1536, 1536, 1536), 1536, "bias", None, None, None),
+             (17, (1536,), 6144, "bias_res", 1, 12, 8), (17, (6144,), 1536, "bias", 1, 6, 4), (17, (1536,), 512, "plain", 1, 1, 8),
+             (16, (1536,), 1536, "bias", 4, 1, 6), (1, (1024,), 512, "bias", 2, 1, 4), (32, (256, 128), 1024, "bias_res", 3, 2, 3),
+             (9, (384,), 1152, "plain", 6, 3, 1), (17, (1536,), 6144, "bias_res", 8, 4, 3)]
+
+
+@pytest.mark.parametrize("case", TCS_CASES, ids=lambda c: "-".join(map(str, c)))
+def test_gemm_packed_weight_streaming_tensor_core(tmp_path, case):
+    """agi_gemm_tcs_bf16 and its cluster variants: packed bf16 weights, up to 32 tokens, one to three matrices side by
+    side, K slices meeting in distributed shared memory, in global slabs, or both."""
+    from aginfer_b200.recipes.layout import pack_kblock_swizzled
+    M, widths, K, epi, cluster, groups, kb = case
+    if kb is not None and cluster * groups * kb < K // 64:
+        kb = -(-K // 64 // (cluster * groups))
+    x = randn(M, K, seed=61)
+    ws = [randn(n, K, seed=62 + i, std=0.02) for i, n in enumerate(widths)]
+    bs = [randn(n, seed=70 + i, std=0.1) for i, n in enumerate(widths)] if "bias" in epi else [None] * len(widths)
+    total = sum(widths)
+    res = randn(M, total, seed=54) if "res" in epi else None
+    act = "gelu_tanh" if "gelu" in epi else None
+    weights = {f"w{i}": pack_kblock_swizzled(w) for i, w in enumerate(ws)}
+    weights.update({f"b{i}": b for i, b in enumerate(bs) if b is not None})
+    inputs = {"x": x, **({"res": res} if res is not None else {})}
+
+    def body(r):
+        parts = [(Weight(f"w{i}"), Weight(f"b{i}") if bs[i] is not None else None, n) for i, n in enumerate(widths)]
+        r.gemm_tcs(Tensor("x"), parts, Tensor("y"), M, K, residual=Tensor("res") if res is not None else None, act=act,
+                   cluster=cluster, groups=groups, kb=kb)
+        r.export_status(Tensor("status"))
+
+    got, _ = run_recipe(tmp_path, weights, inputs, {"y": (BF, (M, total)), "status": (torch.int32, (1,))}, body, repeats=3)
+    assert got["status"].item() == 0, hex(got["status"].item())
+    want = torch.cat([ops.gemm(x, w, bias=b) for w, b in zip(ws, bs)], dim=1)
+    if act or res is not None:
+        want = torch.cat([ops.gemm(x, w, bias=b, residual=None if res is None else res[:, o:o + n], act=act)
+                          for w, b, n, o in zip(ws, bs, widths, [sum(widths[:i]) for i in range(len(widths))])], dim=1)
+    assert ops.max_rel_err(got["y"], want) < 1e-2
