@@ -393,9 +393,10 @@ agi_attention_rows_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, un
 // Tensor-core attention for a handful of query rows (the action head: 17 queries, 17 or 300 keys,
 // head_dim 48).  One block of 8 warps per (head, 16-row tile of queries).  K and V are staged row-major in shared memory (K rows are the
 // "B" operand of Q.K^T as they are, V goes through ldmatrix.trans for P.V); Q stays in registers as the "A" operand.  Each warp
-// takes every eighth pair of 8-key tiles and runs the usual streaming softmax on the m16n8k16 accumulators
-// (scores -> running max / sum per row -> P re-used directly as the A operand of P.V); the eight warps'
-// (max, sum, O) are merged through shared memory at the end.  About 25 MMAs per 16 keys instead of
+// takes every eighth 16-key block, three blocks at a time (their score MMAs are independent: one rescale of the running
+// max / sum per group instead of per block), P re-used directly as the A operand of P.V; the eight warps'
+// (max, sum, O) are merged through shared memory at the end.  With at most 32 keys the warps split the value
+// columns instead of the keys and nothing is merged.  About 25 MMAs per 16 keys instead of
 // thousands of scalar instructions: the kernel is latency-bound, so instruction count is what matters.
 // grid = (q_heads, ceil(q_rows / 16)), block = 256; head_dim a multiple of 16, <= 64.
 // dynamic shared memory = 2 * kv16 * (head_dim + 8) * 2 (K and V) + merge area 8 * 16 * (head_dim + 2) * 4,
@@ -405,7 +406,6 @@ agi_attention_mma_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, uns
                        unsigned q_heads, unsigned kv_heads, unsigned head_dim, unsigned q_stride, unsigned k_stride,
                        unsigned v_stride, unsigned o_stride, float scale, unsigned mask_mode, unsigned mask_arg) {
   extern __shared__ __align__(16) unsigned char attn_smem[];
-  grid_dependency_wait();
   const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
   const unsigned head = blockIdx.x, kv_head = head / (q_heads / kv_heads);
   const unsigned row_base = blockIdx.y * 16;   // this block's query rows
@@ -417,19 +417,28 @@ agi_attention_mma_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, uns
   bf16* v_tile = k_tile + size_t(kv16) * pitch;                    // [kv16][pitch]
   float* merge = reinterpret_cast<float*>(v_tile + size_t(kv16) * pitch);
 
-  // ---- stage K and V with 16-byte asynchronous copies, all in flight at once; rows past kv_rows are zero-filled ----
+  // Keys and values that were written long before the previous kernel (cross-attention over context tokens
+  // projected once per chunk; bit 8 of mask_mode) are requested BEFORE the grid-dependency wait, like weights.
+  const bool early_kv = (mask_mode & 0x100u) != 0;
+  mask_mode &= 0xffu;
+  if (!early_kv) grid_dependency_wait();
+  // ---- stage K and V with 16-byte asynchronous copies, all in flight at once; rows past kv_rows are zero-filled.
+  // Thread t moves 16-byte vector t % 8 of rows t / 8, t / 8 + 32, ... (head_dim <= 64: at most 8 vectors a row).
   const unsigned vec_per_row = head_dim / 8;
-  for (unsigned i = threadIdx.x; i < kv16 * vec_per_row; i += blockDim.x) {
-    const unsigned j = i / vec_per_row, d = (i % vec_per_row) * 8;
-    const unsigned src_row = min(j, kv_rows - 1), bytes = j < kv_rows ? 16u : 0u;
-    const unsigned kd = static_cast<unsigned>(__cvta_generic_to_shared(k_tile + j * pitch + d));
-    const unsigned vd = static_cast<unsigned>(__cvta_generic_to_shared(v_tile + j * pitch + d));
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(kd),
-                 "l"(k + size_t(src_row) * k_stride + kv_head * head_dim + d), "r"(bytes) : "memory");
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vd),
-                 "l"(v + size_t(src_row) * v_stride + kv_head * head_dim + d), "r"(bytes) : "memory");
+  if ((threadIdx.x & 7) < vec_per_row) {
+    const unsigned d = (threadIdx.x & 7) * 8;
+    for (unsigned j = threadIdx.x >> 3; j < kv16; j += blockDim.x >> 3) {
+      const unsigned src_row = min(j, kv_rows - 1), bytes = j < kv_rows ? 16u : 0u;
+      const unsigned kd = static_cast<unsigned>(__cvta_generic_to_shared(k_tile + j * pitch + d));
+      const unsigned vd = static_cast<unsigned>(__cvta_generic_to_shared(v_tile + j * pitch + d));
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(kd),
+                   "l"(k + size_t(src_row) * k_stride + kv_head * head_dim + d), "r"(bytes) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vd),
+                   "l"(v + size_t(src_row) * v_stride + kv_head * head_dim + d), "r"(bytes) : "memory");
+    }
   }
   asm volatile("cp.async.commit_group;" ::: "memory");
+  if (early_kv) grid_dependency_wait();
   // ---- Q fragments (A operand), pre-scaled: rows g, g + 8 of each 16-row tile; zero past q_rows ----
   const unsigned ksteps = head_dim / 16;   // <= 4
   unsigned qa[1][4][4];
@@ -451,43 +460,45 @@ agi_attention_mma_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, uns
   asm volatile("cp.async.wait_group 0;" ::: "memory");
   __syncthreads();
 
-  // running softmax state of this thread's 4 rows (mt 0/1 x rows g, g + 8) and its output accumulators
-  float row_max[1][2], row_sum[1][2], out[1][8][4];
+  // running softmax state of this thread's rows g, g + 8 and its output accumulators (8 dims per tile)
+  float row_max[2], row_sum[2], out[8][4];
+  row_max[0] = row_max[1] = -3.0e38f;
+  row_sum[0] = row_sum[1] = 0.f;
 #pragma unroll
-  for (int mt = 0; mt < 1; ++mt) {
-    row_max[mt][0] = row_max[mt][1] = -3.0e38f;
-    row_sum[mt][0] = row_sum[mt][1] = 0.f;
+  for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) out[mt][nt][i] = 0.f;
-  }
+    for (int i = 0; i < 4; ++i) out[nt][i] = 0.f;
   const unsigned dtiles = head_dim / 8;    // <= 8
+  // Few keys (at most two 16-key blocks, e.g. self-attention over 17 tokens): splitting the keys over warps would
+  // leave six warps idle and still pay the merge.  Instead every warp w < dtiles scores ALL keys (the same few
+  // MMAs in each warp) and multiplies P with the 8 value columns of ITS tile only: no merge, no second barrier,
+  // the warp stores its slice of the output straight from its accumulators.
+  const bool by_dims = kv16 <= 32;
+  if (by_dims && warp >= dtiles) return;
+  const unsigned first_key = by_dims ? 0u : warp * 16u, key_step = by_dims ? 16u : 128u;
+  constexpr int kGroup = 3;   // 16-key blocks scored together: their MMAs are independent, one rescale per group
 
-  for (unsigned key0 = warp * 16; key0 < kv16; key0 += 128) {   // this warp's 16-key blocks
-    // B fragments of K for the two 8-key tiles: b0 = (d 2t..2t+1, key g), b1 = (d 2t+8.., key g)
-    unsigned kb[2][4][2];
+  for (unsigned base = first_key; base < kv16; base += key_step * kGroup) {
+    float s[kGroup][2][4];
 #pragma unroll
-    for (int half = 0; half < 2; ++half)
+    for (int b = 0; b < kGroup; ++b) {
+      const unsigned key0 = base + b * key_step;
 #pragma unroll
-      for (int ks = 0; ks < 4; ++ks)
-        if (ks < ksteps) {
-          const bf16* row = k_tile + (key0 + half * 8 + g) * pitch + ks * 16 + 2 * t;
-          kb[half][ks][0] = *reinterpret_cast<const unsigned*>(row);
-          kb[half][ks][1] = *reinterpret_cast<const unsigned*>(row + 8);
-        }
-#pragma unroll
-    for (int mt = 0; mt < 1; ++mt) {
-      float s[2][4];
+      for (int half = 0; half < 2; ++half) s[b][half][0] = s[b][half][1] = s[b][half][2] = s[b][half][3] = -3.0e38f;
+      if (key0 >= kv16) continue;
+      // B fragments of K for the two 8-key tiles: b0 = (d 2t..2t+1, key g), b1 = (d 2t+8.., key g)
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        s[half][0] = s[half][1] = s[half][2] = s[half][3] = 0.f;
+        s[b][half][0] = s[b][half][1] = s[b][half][2] = s[b][half][3] = 0.f;
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
-          if (ks < ksteps)
-            skinny_mma_bf16(s[half], qa[mt][ks][0], qa[mt][ks][1], qa[mt][ks][2], qa[mt][ks][3], kb[half][ks][0], kb[half][ks][1]);
+          if (ks < ksteps) {
+            const bf16* row = k_tile + (key0 + half * 8 + g) * pitch + ks * 16 + 2 * t;
+            skinny_mma_bf16(s[b][half], qa[0][ks][0], qa[0][ks][1], qa[0][ks][2], qa[0][ks][3],
+                            *reinterpret_cast<const unsigned*>(row), *reinterpret_cast<const unsigned*>(row + 8));
+          }
       }
-      // mask, then per-row maximum over these 16 keys (own 4 values, then across the quad)
+      // mask
 #pragma unroll
       for (int half = 0; half < 2; ++half)
 #pragma unroll
@@ -496,83 +507,117 @@ agi_attention_mma_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, uns
           bool visible = key < kv_rows;
           if (mask_mode == 1) visible = visible && key <= row + mask_arg;
           if (mask_mode == 2) visible = visible && key / mask_arg == row / mask_arg;
-          if (!visible) s[half][i] = -3.0e38f;
+          if (!visible) s[b][half][i] = -3.0e38f;
         }
-      unsigned pa[4];
+    }
+    // per-row maximum over the group's keys (own values, then across the quad), one rescale of the running state
+    unsigned pa[kGroup][4];
 #pragma unroll
-      for (int hr = 0; hr < 2; ++hr) {  // hr 0: row g (c0,c1), hr 1: row g + 8 (c2,c3)
-        float tile_max = fmaxf(fmaxf(s[0][2 * hr], s[0][2 * hr + 1]), fmaxf(s[1][2 * hr], s[1][2 * hr + 1]));
-        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
-        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
-        const float new_max = fmaxf(row_max[mt][hr], tile_max);
-        const float rescale = new_max > -1.0e38f ? __expf(row_max[mt][hr] - new_max) : 1.f;
+    for (int hr = 0; hr < 2; ++hr) {  // hr 0: row g (c0, c1), hr 1: row g + 8 (c2, c3)
+      float group_max = -3.0e38f;
+#pragma unroll
+      for (int b = 0; b < kGroup; ++b)
+        group_max = fmaxf(group_max, fmaxf(fmaxf(s[b][0][2 * hr], s[b][0][2 * hr + 1]), fmaxf(s[b][1][2 * hr], s[b][1][2 * hr + 1])));
+      group_max = fmaxf(group_max, __shfl_xor_sync(0xffffffffu, group_max, 1));
+      group_max = fmaxf(group_max, __shfl_xor_sync(0xffffffffu, group_max, 2));
+      const float new_max = fmaxf(row_max[hr], group_max);
+      const float rescale = new_max > -1.0e38f ? __expf(row_max[hr] - new_max) : 1.f;
+      float group_sum = 0.f;
+#pragma unroll
+      for (int b = 0; b < kGroup; ++b) {
         float p[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float sc = s[j >> 1][2 * hr + (j & 1)];
+          const float sc = s[b][j >> 1][2 * hr + (j & 1)];
           p[j] = sc > -1.0e38f ? __expf(sc - new_max) : 0.f;
         }
-        float tile_sum = (p[0] + p[1]) + (p[2] + p[3]);
-        tile_sum += __shfl_xor_sync(0xffffffffu, tile_sum, 1);
-        tile_sum += __shfl_xor_sync(0xffffffffu, tile_sum, 2);
-        row_sum[mt][hr] = row_sum[mt][hr] * rescale + tile_sum;
-        row_max[mt][hr] = new_max;
-#pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
-          out[mt][nt][2 * hr] *= rescale;
-          out[mt][nt][2 * hr + 1] *= rescale;
-        }
+        group_sum += (p[0] + p[1]) + (p[2] + p[3]);
         // P as the A operand of P.V: a0/a1 = keys 2t..2t+1 (first tile), a2/a3 = keys 2t+8.. (second tile)
         const bf162 lo = __floats2bfloat162_rn(p[0], p[1]), hi = __floats2bfloat162_rn(p[2], p[3]);
-        pa[hr] = *reinterpret_cast<const unsigned*>(&lo);
-        pa[2 + hr] = *reinterpret_cast<const unsigned*>(&hi);
+        pa[b][hr] = *reinterpret_cast<const unsigned*>(&lo);
+        pa[b][2 + hr] = *reinterpret_cast<const unsigned*>(&hi);
       }
-      // O += P (16 x 16 keys) . V (16 keys x 8 dims) per 8-dim tile.  ldmatrix with transpose turns two
-      // 8 x 8 blocks of row-major V (keys 0-7 and 8-15 of this block) into the B fragment (key pair, dim g).
+      group_sum += __shfl_xor_sync(0xffffffffu, group_sum, 1);
+      group_sum += __shfl_xor_sync(0xffffffffu, group_sum, 2);
+      row_sum[hr] = row_sum[hr] * rescale + group_sum;
+      row_max[hr] = new_max;
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        out[nt][2 * hr] *= rescale;
+        out[nt][2 * hr + 1] *= rescale;
+      }
+    }
+    // O += P (16 x 16 keys) . V (16 keys x 8 dims) per 8-dim tile.  ldmatrix with transpose turns two
+    // 8 x 8 blocks of row-major V (keys 0-7 and 8-15 of a block) into the B fragment (key pair, dim g).
+#pragma unroll
+    for (int b = 0; b < kGroup; ++b) {
+      const unsigned key0 = base + b * key_step;
+      if (key0 >= kv16) continue;
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt)
-        if (nt < dtiles) {
+        if (nt < dtiles && (!by_dims || nt == int(warp))) {
           const unsigned addr = static_cast<unsigned>(__cvta_generic_to_shared(v_tile + (key0 + (lane & 15)) * pitch + nt * 8));
           unsigned b0, b1;
           asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(addr));
-          skinny_mma_bf16(out[mt][nt], pa[0], pa[1], pa[2], pa[3], b0, b1);
+          skinny_mma_bf16(out[nt], pa[b][0], pa[b][1], pa[b][2], pa[b][3], b0, b1);
         }
     }
+  }
+
+  if (by_dims) {
+    // this warp's 8 output columns of rows g, g + 8, normalised and stored from the accumulators
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+      if (nt == int(warp)) {
+#pragma unroll
+        for (int hr = 0; hr < 2; ++hr) {
+          const unsigned row = row_base + g + hr * 8;
+          if (row >= q_rows) continue;
+          const float inv = row_sum[hr] > 0.f ? 1.f / row_sum[hr] : 0.f;
+          *reinterpret_cast<bf162*>(o + size_t(row) * o_stride + head * head_dim + nt * 8 + 2 * t) =
+              __floats2bfloat162_rn(out[nt][2 * hr] * inv, out[nt][2 * hr + 1] * inv);
+        }
+      }
+    return;
   }
 
   // ---- merge the eight warps: [warp][row 0..15][head_dim + 2] with max and sum in the last two columns ----
   const unsigned mp = head_dim + 2;
 #pragma unroll
-  for (int mt = 0; mt < 1; ++mt)
+  for (int hr = 0; hr < 2; ++hr) {
+    float* dst = merge + (size_t(warp) * 16 + g + hr * 8) * mp;
 #pragma unroll
-    for (int hr = 0; hr < 2; ++hr) {
-      float* dst = merge + (size_t(warp) * 16 + g + hr * 8) * mp;
-#pragma unroll
-      for (int nt = 0; nt < 8; ++nt)
-        if (nt < dtiles) {
-          dst[nt * 8 + 2 * t] = out[mt][nt][2 * hr];
-          dst[nt * 8 + 2 * t + 1] = out[mt][nt][2 * hr + 1];
-        }
-      if (t == 0) {
-        dst[head_dim] = row_max[mt][hr];
-        dst[head_dim + 1] = row_sum[mt][hr];
+    for (int nt = 0; nt < 8; ++nt)
+      if (nt < dtiles) {
+        dst[nt * 8 + 2 * t] = out[nt][2 * hr];
+        dst[nt * 8 + 2 * t + 1] = out[nt][2 * hr + 1];
       }
+    if (t == 0) {
+      dst[head_dim] = row_max[hr];
+      dst[head_dim + 1] = row_sum[hr];
     }
+  }
   __syncthreads();
-  const unsigned my_rows = min(16u, q_rows - row_base);
-  for (unsigned i = threadIdx.x; i < my_rows * head_dim; i += blockDim.x) {
-    const unsigned r = i / head_dim, d = i % head_dim;
-    float best = -3.0e38f;
-#pragma unroll
-    for (int w = 0; w < 8; ++w) best = fmaxf(best, merge[(w * 16 + r) * mp + head_dim]);
-    float num = 0.f, den = 0.f;
+  // thread = (row, one of 16 column lanes): the eight warps' weights are worked out once per row
+  const unsigned r = threadIdx.x >> 4, c = threadIdx.x & 15;
+  if (row_base + r < q_rows) {
+    float weight[8], best = -3.0e38f, den = 0.f;
 #pragma unroll
     for (int w = 0; w < 8; ++w) {
-      const float* src = merge + (w * 16 + r) * mp;
-      const float f = src[head_dim] > -1.0e38f ? __expf(src[head_dim] - best) : 0.f;
-      num += f * src[d];
-      den += f * src[head_dim + 1];
+      weight[w] = merge[(w * 16 + r) * mp + head_dim];
+      best = fmaxf(best, weight[w]);
     }
-    o[size_t(row_base + r) * o_stride + head * head_dim + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      weight[w] = weight[w] > -1.0e38f ? __expf(weight[w] - best) : 0.f;
+      den += weight[w] * merge[(w * 16 + r) * mp + head_dim + 1];
+    }
+    const float inv = den > 0.f ? 1.f / den : 0.f;
+    for (unsigned d = c; d < head_dim; d += 16) {
+      float num = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) num += weight[w] * merge[(w * 16 + r) * mp + d];
+      o[size_t(row_base + r) * o_stride + head * head_dim + d] = __float2bfloat16_rn(num * inv);
+    }
   }
 }

@@ -36,6 +36,15 @@ enum : unsigned {
 // `grid_dependency_release` lets the successor's blocks be scheduled (they run their own prologue - barrier
 // set-up, weight prefetch - and then block in their own wait until this grid has completed and flushed).
 __device__ __forceinline__ void grid_dependency_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Wait first, release afterwards: the successor (and, transitively, everything after it) cannot start before this
+// grid's predecessors have all completed.  Kernels that release before they wait let later grids cascade into
+// their prologues while much earlier grids are still running, which is harmless for weights but not for data a
+// prologue wants to read that an earlier grid of the same replay wrote; one launch of this kind between the
+// writer and the readers restores the guarantee.
+__device__ __forceinline__ void grid_dependency_wait_then_release() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
 __device__ __forceinline__ void grid_dependency_wait() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // release as early as possible, then wait
   asm volatile("griddepcontrol.wait;" ::: "memory");

@@ -197,9 +197,11 @@ extern "C" __global__ void agi_copy_rows_u32(const unsigned* in, unsigned* out, 
 }
 
 // out[r, :] += addend[r % addend_rows, :]  (positional embeddings, broadcast rows).
+// Releases its successor only after its own wait: recipes run it once per denoising step, after the per-chunk
+// projections and before the blocks, so that a block kernel's prologue may read what those projections wrote.
 extern "C" __global__ void agi_add_rows_bf16(bf16* out, const bf16* addend, unsigned rows, unsigned cols,
                                               unsigned out_stride, unsigned addend_rows) {
-  grid_dependency_wait();
+  grid_dependency_wait_then_release();
   for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < rows * cols; i += gridDim.x * blockDim.x) {
     const unsigned r = i / cols, c = i % cols;
     const float sum = __bfloat162float(out[size_t(r) * out_stride + c]) +

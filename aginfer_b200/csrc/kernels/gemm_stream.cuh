@@ -26,6 +26,7 @@
 #include "common.cuh"
 #include "gemm_simt.cuh"    // gemm_store
 #include "gemm_skinny.cuh"  // mma16n8
+#include "gemm_tc.cuh"      // cluster barrier and distributed-shared-memory helpers
 
 namespace stream {
 
@@ -86,11 +87,17 @@ struct Extra {
   float ln_eps = 0.f;
 };
 
-template <bool kFp8, int NT, bool kLn = false>
+// kSplit > 1: the K range is cut into kSplit slices handled by the CTAs of a thread-block cluster along grid z
+// (K is then the length of ONE slice and `ldw` the row pitch of the weight matrix in elements).  Slice s > 0
+// sends its 16 x M tile of partial sums to slice 0 through distributed shared memory; slice 0 adds them in slice
+// order and runs the epilogue.  A long K thereby becomes kSplit short rings side by side instead of one ring
+// that wraps many times, each wrap a round trip to memory.
+template <bool kFp8, int NT, bool kLn = false, int kSplit = 1>
 __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y, const bf16* bias,
                                      const bf16* residual, const float* scale_a, const float* scale_w,
                                      unsigned* status, unsigned M, unsigned N, unsigned K, unsigned ldx, unsigned ldy,
-                                     unsigned flags, unsigned rows, unsigned chunk_windows, const Extra extra = Extra()) {
+                                     unsigned flags, unsigned rows, unsigned chunk_windows, const Extra extra = Extra(),
+                                     unsigned ldw = 0) {
   constexpr int kConsumerWarps = consumer_warps(NT);
   constexpr int kThreads = threads(NT);
   // dynamic shared memory: ring of slots (rows + M rows each), then the warps' partial tiles
@@ -101,6 +108,9 @@ __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y
   const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
   const unsigned row0 = blockIdx.x * rows;
   const unsigned k_bytes = K * elem;
+  const size_t w_pitch = kSplit > 1 ? size_t(ldw) * elem : size_t(k_bytes);
+  const unsigned split = kSplit > 1 ? blockIdx.z : 0;
+  x += size_t(split) * k_bytes;   // this slice's columns of the activations and (below) of the weights
   const unsigned windows = k_bytes / 64;
   const unsigned chunks = (windows + chunk_windows - 1) / chunk_windows;
   // Slab mode: K is one chunk and both operands are contiguous in global memory, so each arrives with a
@@ -114,6 +124,7 @@ __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y
   const unsigned ring_slots = chunks < unsigned(kSlots) ? chunks : unsigned(kSlots);
   const unsigned mp = M | 1u;  // odd pitch of a partial-tile row: rows land in different banks
   float* partial = reinterpret_cast<float*>(ring + ((ring_slots * slot_bytes + 15u) & ~15u));  // [warp][16][mp]
+  float* gathered = partial + kConsumerWarps * 16 * mp;   // [slice - 1][rows * M], written by the other slices
   // Which of the side-by-side weight matrices this CTA's rows belong to.
   unsigned seg_rows = N, local0 = row0, col0 = 0;
   const uint8_t* w_seg = w;
@@ -134,6 +145,7 @@ __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  if (kSplit > 1) tc::cluster_arrive();   // "this slice is running": waited for before anyone stores into it
 
   // Each thread's first output element (i = threadIdx.x): its bias and residual are fetched early, as soon
   // as the previous kernel's results are known to be visible, and used after the reduction.
@@ -166,10 +178,10 @@ __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y
       if (lane == 0) expect_bytes(bar, bytes * ((slab ? live_rows : rows) + M + mod_rows));
       __syncwarp();
       if (slab) {
-        if (lane == 0) bulk_copy(base, w_seg + size_t(local0) * k_bytes, bytes * live_rows, bar);
+        if (lane == 0) bulk_copy(base, w_seg + size_t(local0) * w_pitch, bytes * live_rows, bar);
       } else
       for (unsigned r = lane; r < rows; r += 32)  // rows past N re-read the last row; their results are dropped
-        bulk_copy(base + r * pitch, w_seg + size_t(min(local0 + r, seg_rows - 1)) * k_bytes + size_t(first) * 64, bytes, bar);
+        bulk_copy(base + r * pitch, w_seg + size_t(min(local0 + r, seg_rows - 1)) * w_pitch + size_t(split) * k_bytes + size_t(first) * 64, bytes, bar);
       if (!waited && (c + 1 == kSlots || c + 1 == chunks)) {
         // The weight copies of the first slots are in flight; only now wait for the previous kernel,
         // then fetch the activations it produced for those slots.
@@ -321,6 +333,22 @@ __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y
   }
   grid_dependency_release();
   __syncthreads();
+  if (kSplit > 1) {
+    tc::cluster_wait();   // every slice of the cluster is running
+    if (split != 0) {
+      const unsigned cell0 = tc::peer_smem(smem_u32(gathered + (split - 1) * rows * M), 0);
+      for (unsigned i = threadIdx.x; i < rows * M; i += kThreads) {
+        const unsigned r = i % rows, m = i / rows;
+        float total = 0.f;
+#pragma unroll
+        for (int wq = 0; wq < kConsumerWarps; ++wq) total += partial[(wq * 16 + r) * mp + m];
+        tc::store_peer_f32(cell0 + i * 4, total);
+      }
+    }
+    tc::cluster_arrive();
+    tc::cluster_wait();   // the partial sums of every slice have landed in slice 0
+    if (split != 0) return;
+  }
   const float alpha = (flags & kFlagScaled) ? (*scale_a) * (*scale_w) : 1.f;
   for (unsigned i = threadIdx.x; i < rows * M; i += kThreads) {
     const unsigned r = i % rows, m = i / rows;
@@ -328,6 +356,8 @@ __device__ __forceinline__ void body(const uint8_t* x, const uint8_t* w, void* y
     float total = 0.f;
 #pragma unroll
     for (int wq = 0; wq < kConsumerWarps; ++wq) total += partial[(wq * 16 + r) * mp + m];
+#pragma unroll
+    for (int s = 1; s < kSplit; ++s) total += gathered[(s - 1) * rows * M + i];   // slice order
     // bias is indexed inside its own matrix, the output column across all of them
     const unsigned n = col0 + local0 + r;
     if (i == threadIdx.x && early_valid) {
@@ -396,6 +426,27 @@ AGI_STREAM_FUSED_KERNEL(agi_gemm_stream_lnfused_bf16_t6, 6, true)
 AGI_STREAM_FUSED_KERNEL(agi_gemm_stream_fused_bf16_t8, 8, false)
 AGI_STREAM_FUSED_KERNEL(agi_gemm_stream_lnfused_bf16_t8, 8, true)
 #undef AGI_STREAM_FUSED_KERNEL
+
+// K slices in a cluster of S CTAs along grid z: grid = (ceil(N / rows), 1, S); K = elements per slice, ldw = row
+// pitch of w in elements (S * K); shared memory as above for the slice, + (S - 1) * rows * M * 4.
+#define AGI_STREAM_SPLIT_KERNEL(NAME, NT, S)                                                                          \
+  extern "C" __global__ void __cluster_dims__(1, 1, S) __launch_bounds__(stream::threads(NT), 3)                     \
+  NAME(const bf16* x, const bf16* w, void* y, const bf16* bias, const bf16* residual, unsigned* status, unsigned M,  \
+       unsigned N, unsigned K, unsigned ldx, unsigned ldy, unsigned flags, unsigned rows, unsigned chunk_windows,   \
+       unsigned ldw) {                                                                                               \
+    stream::body<false, NT, false, S>(reinterpret_cast<const uint8_t*>(x), reinterpret_cast<const uint8_t*>(w), y,   \
+                                      bias, residual, nullptr, nullptr, status, M, N, K, ldx, ldy, flags, rows,     \
+                                      chunk_windows, stream::Extra(), ldw);                                          \
+  }
+AGI_STREAM_SPLIT_KERNEL(agi_gemm_stream_bf16_t1_k2, 1, 2)
+AGI_STREAM_SPLIT_KERNEL(agi_gemm_stream_bf16_t2_k2, 2, 2)
+AGI_STREAM_SPLIT_KERNEL(agi_gemm_stream_bf16_t3_k2, 3, 2)
+AGI_STREAM_SPLIT_KERNEL(agi_gemm_stream_bf16_t4_k2, 4, 2)
+AGI_STREAM_SPLIT_KERNEL(agi_gemm_stream_bf16_t1_k4, 1, 4)
+AGI_STREAM_SPLIT_KERNEL(agi_gemm_stream_bf16_t2_k4, 2, 4)
+AGI_STREAM_SPLIT_KERNEL(agi_gemm_stream_bf16_t3_k4, 3, 4)
+AGI_STREAM_SPLIT_KERNEL(agi_gemm_stream_bf16_t4_k4, 4, 4)
+#undef AGI_STREAM_SPLIT_KERNEL
 
 AGI_STREAM_KERNEL(agi_gemm_stream_bf16_t1, bf16, false, 1)
 AGI_STREAM_KERNEL(agi_gemm_stream_bf16_t2, bf16, false, 2)

@@ -246,21 +246,27 @@ def tcs_tiling(M: int, tiles: int, K: int, cluster: int | None = None, groups: i
             "shared_bytes": kb * 20480 + 1024 + gather}
 
 
-def stream_tiling(M: int, N: int, K: int, elem: int, extra_rows: int = 0, contiguous: bool = True) -> dict[str, int]:
+STREAM_SPLITS = (4, 2)          # compiled cluster sizes of agi_gemm_stream_bf16_t{1..4}_k{S}
+
+
+def stream_tiling(M: int, N: int, K: int, elem: int, extra_rows: int = 0, contiguous: bool = True,
+                  splits: int = 1) -> dict[str, int]:
     """Launch geometry of ``agi_gemm_stream_*``: rows per CTA, K windows per ring slot, slots.
 
     Aim: at least one CTA per SM when N allows it, every CTA resident at once (one wave), and the shared
     memory of an SM split evenly between the CTAs that share it, so that as many bytes as possible are
     in flight.  16 rows per CTA halve the activation traffic per weight byte and are used when N is large
-    enough to still give every SM a CTA."""
-    rows = 16 if ceil_div(N, 16) >= STREAM_MIN_CTAS_FOR_16_ROWS else 8
+    enough to still give every SM a CTA.  ``splits`` > 1: K is cut into that many slices, one CTA of a
+    thread-block cluster each (the geometry is that of one slice; ``grid`` stays the number of row groups)."""
+    rows = 16 if ceil_div(N, 16) * splits >= STREAM_MIN_CTAS_FOR_16_ROWS else 8
     grid = ceil_div(N, rows)
-    per_sm = ceil_div(grid, SM_COUNT)
+    per_sm = ceil_div(grid * splits, SM_COUNT)
     tiles = next(v for v in (1, 2, 3, 4, 6, 8) if 8 * v >= M)
     warps = 4                                           # consumer warps (plus one producer warp)
     tail = 16 + warps * 16 * (M | 1) * 4                # alignment slack + the warps' partial tiles
+    tail += (splits - 1) * rows * M * 4                 # + the other slices' partial sums, gathered by slice 0
     budget = min(STREAM_CTA_BYTES, STREAM_SM_BYTES // per_sm) - tail
-    windows = K * elem // 64
+    windows = K // splits * elem // 64
     row_bytes = lambda w: w * 64 + 16
     held = rows + M + extra_rows   # rows of a ring slot: weights, activations
     common = {"rows": rows, "grid": grid, "tiles": tiles, "threads": (warps + 1) * 32}
@@ -274,6 +280,22 @@ def stream_tiling(M: int, N: int, K: int, elem: int, extra_rows: int = 0, contig
         slots = 2
     return {**common, "chunk_windows": chunk_windows, "slots": slots, "slab": False,
             "shared_bytes": slots * held * row_bytes(chunk_windows) + tail}
+
+
+def stream_splits(M: int, N: int, K: int, elem: int) -> int:
+    """K slices for the bulk-stream GEMM.  One ring that wraps many times pays a round trip to memory per wrap
+    (1536 x 6144 at 17 tokens: six chunks through two slots, 10.5 us); the same matrix as four slices side by
+    side, each the shape of a 1536-wide product, has nothing to wait for twice.  Slices are used when the single
+    ring would need more than four chunks and the sliced grid still fits three CTAs per SM."""
+    if elem != 2 or M > 32:
+        return 1
+    t = stream_tiling(M, N, K, elem)
+    if ceil_div(K * elem // 64, t["chunk_windows"]) <= 4:
+        return 1
+    for s in STREAM_SPLITS:
+        if K % (s * 32) == 0 and ceil_div(N, 16) * s <= 3 * SM_COUNT:
+            return s
+    return 1
 
 
 # ---- persistent block kernel (csrc/kernels/dit_block.cuh) ------------------------------------------------
@@ -405,6 +427,16 @@ class RecipeBuilder:
         entry = self.tactics.setdefault(key, {"op": key[0], "algorithm": key[1], "kernel": kernel, "uses": 0, **tactic})
         entry["uses"] += 1
 
+    def launch_count(self) -> int:
+        assert self._profile is not None, "begin_profile first"
+        return len(self._profile.launches)
+
+    def drop_launches(self, first: int, kernel: str) -> None:
+        """Remove the launches of ``kernel`` emitted since ``launch_count()`` returned ``first`` (measurement
+        profiles that replay a sub-sequence of another profile's launches exactly as that profile emits them)."""
+        assert self._profile is not None, "begin_profile first"
+        self._profile.launches[first:] = [l for l in self._profile.launches[first:] if l["kernel"] != kernel]
+
     # ---- kernel families ------------------------------------------------------------------
     def export_status(self, out: Pointer) -> None:
         """Copy the status word (0 = every bounded wait succeeded) into a caller-visible I32 tensor."""
@@ -473,9 +505,12 @@ class RecipeBuilder:
     def attention(self, q: Pointer, k: Pointer, v: Pointer, o: Pointer, *, q_rows: int, kv_rows: int, q_heads: int,
                   kv_heads: int, head_dim: int, q_stride: int, k_stride: int, v_stride: int, o_stride: int,
                   mask: str = "none", mask_arg: int = 0, scale: float | None = None,
-                  algorithm: str = "auto", amax: Pointer | None = None) -> None:
+                  algorithm: str = "auto", amax: Pointer | None = None, kv_static: bool = False) -> None:
         """``amax`` (a ``counter()`` slot; head widths 80 and 128, streaming tensor-core kernel only): the kernel
-        also leaves max |o| there for a following ``quantize_e4m3(..., amax=)``."""
+        also leaves max |o| there for a following ``quantize_e4m3(..., amax=)``.
+        ``kv_static``: keys and values were written before the last ``agi_add_rows_bf16`` launch of the profile
+        (which releases its successors only after its own wait), not by the launches since; the few-query-rows
+        kernel then requests them before its grid-dependency wait."""
         assert head_dim <= 128 and head_dim % 2 == 0 and q_heads % kv_heads == 0
         mode = {"none": 0, "causal": 1, "block": 2}[mask]
         args = [q, k, v, o, U32(q_rows), U32(kv_rows), U32(q_heads), U32(kv_heads), U32(head_dim), U32(q_stride),
@@ -490,11 +525,13 @@ class RecipeBuilder:
                      + q_rows * ceil_div(kv_rows, 32) * 32 * 4 + 8 * q_rows * head_dim * 4 + 2 * 8 * q_rows * 4)
         kv16 = ceil_div(kv_rows, 16) * 16
         mma_smem = 2 * kv16 * (head_dim + 8) * 2 + 8 * 16 * (head_dim + 2) * 4
-        if (aligned and q_rows <= 64 and head_dim <= 64 and head_dim % 16 == 0 and q_stride % 2 == 0
+        if (aligned and q_rows <= 64 and head_dim <= 64 and head_dim % 16 == 0 and q_stride % 2 == 0 and o_stride % 2 == 0
                 and mma_smem <= ATTN_SMEM_BUDGET and algorithm in ("auto", "mma")):
             # few query rows: one block per head, tensor-core scores and P.V
+            if kv_static:
+                args = args[:14] + [U32(mode | 0x100), args[15]]
             self.launch("agi_attention_mma_bf16", (q_heads, ceil_div(q_rows, 16), 1), (256, 1, 1), args, shared_bytes=mma_smem,
-                        op=f"attention_{mask}", algorithm="mma_key_split")
+                        op=f"attention_{mask}", algorithm="mma_key_split" + ("_early_kv" if kv_static else ""))
             return
         # streaming tensor-core kernel: 4, 2 or 1 warps (64, 32 or 16 query rows) per block, the most rows that still
         # give the grid about one block per SM
@@ -613,6 +650,15 @@ class RecipeBuilder:
             # both operands reach shared memory by bulk copies; K is cut into chunks of <= ~100 KB per slot
             if M > 64 or (K * elem) % 64 or not aligned:
                 raise ValueError("stream GEMM needs M <= 64, K bytes % 64 == 0 and 16-byte aligned rows")
+            S = stream_splits(M, N, K, elem) if dtype == "bf16" and not out_f32 and scale_a is None else 1
+            if S > 1:
+                t = stream_tiling(M, N, K, elem, splits=S)
+                self.launch(f"agi_gemm_stream_bf16_t{t['tiles']}_k{S}", (t["grid"], 1, S), (t["threads"], 1, 1),
+                            [x, w, y, bias or dummy, residual or dummy, Arena(STATUS_WORD), U32(M), U32(N), U32(K // S),
+                             U32(ldx or K), U32(ldy or N), U32(flags), U32(t["rows"]), U32(t["chunk_windows"]), U32(K)],
+                            shared_bytes=t["shared_bytes"], op="gemm_bf16",
+                            algorithm=f"bulk_stream_r{t['rows']}_t{t['tiles']}_c{t['chunk_windows']}_k{S}")
+                return
             t = stream_tiling(M, N, K, elem, contiguous=(ldx or K) == K)
             rows, chunk_windows, tiles = t["rows"], t["chunk_windows"], t["tiles"]
             if t["slab"]:

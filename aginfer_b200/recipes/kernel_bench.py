@@ -76,7 +76,8 @@ def build(case: str, tactic: str, reps: int, tokens: int, stages: int = 4, dtype
         elif case in ("attn_self", "attn_cross"):
             kv_rows = tokens if case == "attn_self" else 300
             r.attention(q, kbuf, vbuf, y, q_rows=tokens, kv_rows=kv_rows, q_heads=32, kv_heads=32, head_dim=48,
-                        q_stride=D, k_stride=D, v_stride=D, o_stride=D)
+                        q_stride=D, k_stride=D, v_stride=D, o_stride=D,
+                        algorithm=tactic if tactic in ("warp_per_row", "keys_in_smem", "mma") else "auto")
         elif case == "attn_prefill":      # decoder prefill: `tokens` causal rows, 16 query / 2 KV heads of 128
             r.attention(q, kbuf, vbuf, y, q_rows=tokens, kv_rows=tokens, q_heads=16, kv_heads=2, head_dim=128,
                         q_stride=2048, k_stride=256, v_stride=256, o_stride=2048, mask="causal")

@@ -348,7 +348,8 @@ def roofline_of_stream_gemm(context, harness, session_flags, peak) -> dict:
                        "algorithmic bytes per launch",
         "launches": launches, "avg_launch_us": stream_ms * 1000.0 / launches,
         "algorithmic_bytes_per_launch": total_bytes / launches,
-        "how": "the GEMM launches of one denoising step replayed back to back (profile gemm_stream), CUDA events",
+        "how": "the weight-streaming GEMM launches of one denoising step replayed back to back, without the other "
+               "kernels of the step (profile gemm_stream), CUDA events",
         "status_word": int(status.item()),
     }
 

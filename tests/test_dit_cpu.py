@@ -1,4 +1,5 @@
 """DiT recipe: structure checks on CPU (no GPU), and the oracle's own invariants on a tiny shape."""
+import pytest
 import torch
 
 from aginfer_b200 import planfmt

@@ -65,7 +65,7 @@ def test_full_size_action_chunk_matches_oracle(tmp_path, block_kernel, packed):
           f"launches/chunk={stats['launches_per_enqueue']}")
     assert cos >= 0.999 and err < 2e-2
     # a fresh session reproduces the chunk bit for bit: partial sums are added in a fixed order
-    again, _ = run_chunk(tmp_path / "again", cfg, w, x, repeats=1, block_kernel=block_kernel)
+    again, _ = run_chunk(tmp_path / "again", cfg, w, x, repeats=1, block_kernel=block_kernel, packed=packed)
     assert torch.equal(again, got)
 
 

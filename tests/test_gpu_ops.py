@@ -525,6 +525,9 @@ SKINNY_CASES = [
     (4, 3072, 1536, "bf16", "bias"), (1, 1024, 64, "bf16", "bias"), (16, 1536, 32, "bf16", "bias"),
     (16, 32, 1024, "bf16", "bias"), (50, 1024, 4096, "bf16", "plain"), (64, 4096, 1024, "bf16", "plain"),
     (33, 100, 96, "bf16", "bias"),
+    # long K: the bulk-stream tactic cuts these into 4 (or, 4160 = 65 x 64, 2) slices over a thread-block cluster
+    (9, 256, 8192, "bf16", "bias_gelu"), (1, 128, 16384, "bf16", "plain"), (25, 520, 4096, "bf16", "bias_res"),
+    (17, 1536, 4160, "bf16", "bias_res"),
     (1, 2048, 2048, "e4m3", "plain"), (16, 11008, 2048, "e4m3", "plain"), (64, 2048, 11008, "e4m3", "bias"),
     (64, 2560, 2048, "e4m3", "plain"), (16, 1536, 1536, "e4m3", "plain"), (1, 6144, 1536, "e4m3", "plain"),
 ]
