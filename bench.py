@@ -340,7 +340,7 @@ def roofline_of_stream_gemm(context, harness, session_flags, peak) -> dict:
     achieved = total_bytes / (stream_ms / 1000.0) / 1e9
     ratio = measured_traffic_ratio()
     return {
-        "bound": "hbm", "kernel": "agi_gemm_stream_bf16_t3 / agi_gemm_stream_fused_bf16_t3", "achieved": achieved,
+        "bound": "hbm", "kernel": "agi_gemm_stream_bf16_t3 / agi_gemm_stream_bf16_t3_k4 / agi_gemm_stream_fused_bf16_t3", "achieved": achieved,
         "peak": peak["hbm_gbs"], "unit": "GB/s", "frac": achieved / peak["hbm_gbs"], "peak_kind": f"of {peak['kind']}",
         "traffic": None if ratio is None else ratio * total_bytes / launches,
         "traffic_how": "ncu dram__bytes_read.sum + dram__bytes_write.sum of the 6144x1536 and 1536x6144 launches "
