@@ -574,6 +574,11 @@ def main() -> None:
     parser.add_argument("--legs", default="all", choices=["all", "device"],
                         help="'device' runs only the device-resident timed leg (small profiler captures)")
     args = parser.parse_args()
+    if int(os.environ.get("RANK", "0")) == 0:
+        # torch.distributed.run exports OMP_NUM_THREADS=1 to every rank; rank 0 also times the CPU oracle, which is
+        # meant to use every host thread (torch is imported only after this point)
+        for name in ("OMP_NUM_THREADS", "MKL_NUM_THREADS"):
+            os.environ[name] = str(os.cpu_count() or 1)
     if args.impl == "reference":
         run_reference(args)
     else:
