@@ -398,13 +398,14 @@ agi_attention_rows_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, un
 // (max, sum, O) are merged through shared memory at the end.  With at most 32 keys the warps split the value
 // columns instead of the keys and nothing is merged.  About 25 MMAs per 16 keys instead of
 // thousands of scalar instructions: the kernel is latency-bound, so instruction count is what matters.
-// grid = (q_heads, ceil(q_rows / 16)), block = 256; head_dim a multiple of 16, <= 64.
+// grid = (q_heads, ceil(q_rows / 16)), block = 256; head_dim a multiple of 16, <= 64 (agi_attention_mma_bf16_d128: <= 128).
 // dynamic shared memory = 2 * kv16 * (head_dim + 8) * 2 (K and V) + merge area 8 * 16 * (head_dim + 2) * 4,
 // kv16 = kv_rows rounded up to 16.
-extern "C" __global__ void __launch_bounds__(256)
-agi_attention_mma_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, unsigned q_rows, unsigned kv_rows,
-                       unsigned q_heads, unsigned kv_heads, unsigned head_dim, unsigned q_stride, unsigned k_stride,
-                       unsigned v_stride, unsigned o_stride, float scale, unsigned mask_mode, unsigned mask_arg) {
+template <int kKsteps, int kDtiles, bool kAliasMerge>
+__device__ __forceinline__ void attention_mma_body(const bf16* q, const bf16* k, const bf16* v, bf16* o, unsigned q_rows,
+                                                   unsigned kv_rows, unsigned q_heads, unsigned kv_heads, unsigned head_dim,
+                                                   unsigned q_stride, unsigned k_stride, unsigned v_stride, unsigned o_stride,
+                                                   float scale, unsigned mask_mode, unsigned mask_arg) {
   extern __shared__ __align__(16) unsigned char attn_smem[];
   const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
   const unsigned head = blockIdx.x, kv_head = head / (q_heads / kv_heads);
@@ -415,19 +416,23 @@ agi_attention_mma_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, uns
   const unsigned pitch = head_dim + 8;
   bf16* k_tile = reinterpret_cast<bf16*>(attn_smem);               // [kv16][pitch]
   bf16* v_tile = k_tile + size_t(kv16) * pitch;                    // [kv16][pitch]
-  float* merge = reinterpret_cast<float*>(v_tile + size_t(kv16) * pitch);
+  // the merge area follows the tiles, or (kAliasMerge: wide heads, where both would not fit) re-uses their space
+  // once every warp is done with keys and values
+  float* merge = kAliasMerge ? reinterpret_cast<float*>(attn_smem) : reinterpret_cast<float*>(v_tile + size_t(kv16) * pitch);
 
   // Keys and values that were written long before the previous kernel (cross-attention over context tokens
-  // projected once per chunk; bit 8 of mask_mode) are requested BEFORE the grid-dependency wait, like weights.
+  // projected once per chunk, the prefix of a KV cache; bit 8 of mask_mode, bits 16-31 = how many leading rows,
+  // 0 = all) are requested BEFORE the grid-dependency wait, like weights; the rest after it.
   const bool early_kv = (mask_mode & 0x100u) != 0;
+  const unsigned static_rows = !early_kv ? 0u : ((mask_mode >> 16) != 0 ? min(mask_mode >> 16, kv_rows) : kv16);
   mask_mode &= 0xffu;
-  if (!early_kv) grid_dependency_wait();
   // ---- stage K and V with 16-byte asynchronous copies, all in flight at once; rows past kv_rows are zero-filled.
-  // Thread t moves 16-byte vector t % 8 of rows t / 8, t / 8 + 32, ... (head_dim <= 64: at most 8 vectors a row).
+  // Thread t moves 16-byte vector t % kDtiles of rows t / kDtiles, t / kDtiles + 256 / kDtiles, ...
   const unsigned vec_per_row = head_dim / 8;
-  if ((threadIdx.x & 7) < vec_per_row) {
-    const unsigned d = (threadIdx.x & 7) * 8;
-    for (unsigned j = threadIdx.x >> 3; j < kv16; j += blockDim.x >> 3) {
+  auto stage = [&](unsigned first, unsigned last) {
+    if ((threadIdx.x % kDtiles) >= vec_per_row) return;
+    const unsigned d = (threadIdx.x % kDtiles) * 8;
+    for (unsigned j = first + threadIdx.x / kDtiles; j < last; j += blockDim.x / kDtiles) {
       const unsigned src_row = min(j, kv_rows - 1), bytes = j < kv_rows ? 16u : 0u;
       const unsigned kd = static_cast<unsigned>(__cvta_generic_to_shared(k_tile + j * pitch + d));
       const unsigned vd = static_cast<unsigned>(__cvta_generic_to_shared(v_tile + j * pitch + d));
@@ -436,16 +441,18 @@ agi_attention_mma_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, uns
       asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vd),
                    "l"(v + size_t(src_row) * v_stride + kv_head * head_dim + d), "r"(bytes) : "memory");
     }
-  }
+  };
+  stage(0, static_rows);
+  grid_dependency_wait();
+  stage(static_rows, kv16);
   asm volatile("cp.async.commit_group;" ::: "memory");
-  if (early_kv) grid_dependency_wait();
   // ---- Q fragments (A operand), pre-scaled: rows g, g + 8 of each 16-row tile; zero past q_rows ----
-  const unsigned ksteps = head_dim / 16;   // <= 4
-  unsigned qa[1][4][4];
+  const unsigned ksteps = head_dim / 16;   // <= kKsteps
+  unsigned qa[1][kKsteps][4];
 #pragma unroll
   for (int mt = 0; mt < 1; ++mt)
 #pragma unroll
-    for (int ks = 0; ks < 4; ++ks)
+    for (int ks = 0; ks < kKsteps; ++ks)
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
         qa[mt][ks][r] = 0;
@@ -461,19 +468,19 @@ agi_attention_mma_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, uns
   __syncthreads();
 
   // running softmax state of this thread's rows g, g + 8 and its output accumulators (8 dims per tile)
-  float row_max[2], row_sum[2], out[8][4];
+  float row_max[2], row_sum[2], out[kDtiles][4];
   row_max[0] = row_max[1] = -3.0e38f;
   row_sum[0] = row_sum[1] = 0.f;
 #pragma unroll
-  for (int nt = 0; nt < 8; ++nt)
+  for (int nt = 0; nt < kDtiles; ++nt)
 #pragma unroll
     for (int i = 0; i < 4; ++i) out[nt][i] = 0.f;
-  const unsigned dtiles = head_dim / 8;    // <= 8
+  const unsigned dtiles = head_dim / 8;    // <= kDtiles
   // Few keys (at most two 16-key blocks, e.g. self-attention over 17 tokens): splitting the keys over warps would
   // leave six warps idle and still pay the merge.  Instead every warp w < dtiles scores ALL keys (the same few
   // MMAs in each warp) and multiplies P with the 8 value columns of ITS tile only: no merge, no second barrier,
   // the warp stores its slice of the output straight from its accumulators.
-  const bool by_dims = kv16 <= 32;
+  const bool by_dims = kv16 <= 32 && dtiles <= 8;   // eight warps: one value tile each
   if (by_dims && warp >= dtiles) return;
   const unsigned first_key = by_dims ? 0u : warp * 16u, key_step = by_dims ? 16u : 128u;
   constexpr int kGroup = 3;   // 16-key blocks scored together: their MMAs are independent, one rescale per group
@@ -491,7 +498,7 @@ agi_attention_mma_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, uns
       for (int half = 0; half < 2; ++half) {
         s[b][half][0] = s[b][half][1] = s[b][half][2] = s[b][half][3] = 0.f;
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
+        for (int ks = 0; ks < kKsteps; ++ks)
           if (ks < ksteps) {
             const bf16* row = k_tile + (key0 + half * 8 + g) * pitch + ks * 16 + 2 * t;
             skinny_mma_bf16(s[b][half], qa[0][ks][0], qa[0][ks][1], qa[0][ks][2], qa[0][ks][3],
@@ -542,7 +549,7 @@ agi_attention_mma_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, uns
       row_sum[hr] = row_sum[hr] * rescale + group_sum;
       row_max[hr] = new_max;
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
+      for (int nt = 0; nt < kDtiles; ++nt) {
         out[nt][2 * hr] *= rescale;
         out[nt][2 * hr + 1] *= rescale;
       }
@@ -554,7 +561,7 @@ agi_attention_mma_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, uns
       const unsigned key0 = base + b * key_step;
       if (key0 >= kv16) continue;
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt)
+      for (int nt = 0; nt < kDtiles; ++nt)
         if (nt < dtiles && (!by_dims || nt == int(warp))) {
           const unsigned addr = static_cast<unsigned>(__cvta_generic_to_shared(v_tile + (key0 + (lane & 15)) * pitch + nt * 8));
           unsigned b0, b1;
@@ -567,7 +574,7 @@ agi_attention_mma_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, uns
   if (by_dims) {
     // this warp's 8 output columns of rows g, g + 8, normalised and stored from the accumulators
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt)
+    for (int nt = 0; nt < kDtiles; ++nt)
       if (nt == int(warp)) {
 #pragma unroll
         for (int hr = 0; hr < 2; ++hr) {
@@ -583,11 +590,12 @@ agi_attention_mma_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, uns
 
   // ---- merge the eight warps: [warp][row 0..15][head_dim + 2] with max and sum in the last two columns ----
   const unsigned mp = head_dim + 2;
+  if (kAliasMerge) __syncthreads();   // nobody reads keys or values any more: their space becomes the merge area
 #pragma unroll
   for (int hr = 0; hr < 2; ++hr) {
     float* dst = merge + (size_t(warp) * 16 + g + hr * 8) * mp;
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt)
+    for (int nt = 0; nt < kDtiles; ++nt)
       if (nt < dtiles) {
         dst[nt * 8 + 2 * t] = out[nt][2 * hr];
         dst[nt * 8 + 2 * t + 1] = out[nt][2 * hr + 1];
@@ -620,4 +628,25 @@ agi_attention_mma_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, uns
       o[size_t(row_base + r) * o_stride + head * head_dim + d] = __float2bfloat16_rn(num * inv);
     }
   }
+}
+
+extern "C" __global__ void __launch_bounds__(256)
+agi_attention_mma_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, unsigned q_rows, unsigned kv_rows,
+                       unsigned q_heads, unsigned kv_heads, unsigned head_dim, unsigned q_stride, unsigned k_stride,
+                       unsigned v_stride, unsigned o_stride, float scale, unsigned mask_mode, unsigned mask_arg) {
+  attention_mma_body<4, 8, false>(q, k, v, o, q_rows, kv_rows, q_heads, kv_heads, head_dim, q_stride, k_stride, v_stride,
+                                  o_stride, scale, mask_mode, mask_arg);
+}
+
+// The same for heads up to 128 wide (a 50-token action expert over a 256-token prefix: 8 heads of 128).  The streaming
+// kernel gives each warp ALL keys of its 16 query rows (640 dependent MMAs at these sizes, with 8 CTAs on the whole
+// part); here 8 warps x ceil(q_rows / 16) x heads CTAs split the keys.  Keys, values and the merge area do not fit
+// side by side, so the merge re-uses the tiles' space: dynamic shared memory =
+// max(2 * kv16 * (head_dim + 8) * 2, 8 * 16 * (head_dim + 2) * 4).
+extern "C" __global__ void __launch_bounds__(256)
+agi_attention_mma_bf16_d128(const bf16* q, const bf16* k, const bf16* v, bf16* o, unsigned q_rows, unsigned kv_rows,
+                            unsigned q_heads, unsigned kv_heads, unsigned head_dim, unsigned q_stride, unsigned k_stride,
+                            unsigned v_stride, unsigned o_stride, float scale, unsigned mask_mode, unsigned mask_arg) {
+  attention_mma_body<8, 16, true>(q, k, v, o, q_rows, kv_rows, q_heads, kv_heads, head_dim, q_stride, k_stride, v_stride,
+                                  o_stride, scale, mask_mode, mask_arg);
 }

@@ -651,6 +651,35 @@ AGI_TC_GROUP_KERNEL(agi_gemm_tc_e4m3_x3, uint8_t, true, false)
 AGI_TC_GROUP_KERNEL(agi_gemm_tcp_e4m3_x3, uint8_t, true, true)
 #undef AGI_TC_GROUP_KERNEL
 
+// The grouped launch with K slices in a thread-block cluster (up to 64 tokens, bf16): grid = (sum of ceil(N_i / 128),
+// 1, C), cluster (1, 1, C); the slices of a tile exchange partial sums through distributed shared memory as in
+// agi_gemm_tc_bf16_c*.  Three small projections of one layer (queries | keys | values, gate | up) become one launch.
+// Dynamic shared memory = stages * (16384 + TN * 128) + 1024 + C * ceil(TN / C) * 512.
+#define AGI_TC_GROUP_CLUSTER_KERNEL(NAME, C)                                                                          \
+  extern "C" __global__ void __cluster_dims__(1, 1, C) __launch_bounds__(tc::kThreads, 1)                            \
+  NAME(const bf16* x, const float* scale_a, unsigned* status, unsigned M, unsigned K, unsigned ldx, unsigned flags,   \
+       unsigned TN, unsigned stages, const bf16* w0, const bf16* bias0, const float* sw0, void* y0, unsigned N0,      \
+       unsigned ldy0, const bf16* w1, const bf16* bias1, const float* sw1, void* y1, unsigned N1, unsigned ldy1,      \
+       const bf16* w2, const bf16* bias2, const float* sw2, void* y2, unsigned N2, unsigned ldy2) {                   \
+    const unsigned t0 = (N0 + tc::kTileN - 1) / tc::kTileN, t1 = (N1 + tc::kTileN - 1) / tc::kTileN;                  \
+    const bf16* w = w0;                                                                                               \
+    const bf16* bias = bias0;                                                                                         \
+    void* y = y0;                                                                                                     \
+    unsigned N = N0, ldy = ldy0, tile = blockIdx.x;                                                                   \
+    if (tile >= t0 + t1) {                                                                                            \
+      w = w2; bias = bias2; y = y2; N = N2; ldy = ldy2; tile -= t0 + t1;                                              \
+    } else if (tile >= t0) {                                                                                          \
+      w = w1; bias = bias1; y = y1; N = N1; ldy = ldy1; tile -= t0;                                                   \
+    }                                                                                                                 \
+    tc::gemm_body<false, C, false>(reinterpret_cast<const uint8_t*>(x), reinterpret_cast<const uint8_t*>(w), y, bias, \
+                                   bias, nullptr, nullptr, nullptr, nullptr, status, M, N, K, ldx, ldy, flags, TN,    \
+                                   stages, tile);                                                                     \
+  }
+AGI_TC_GROUP_CLUSTER_KERNEL(agi_gemm_tc_bf16_x3_c2, 2)
+AGI_TC_GROUP_CLUSTER_KERNEL(agi_gemm_tc_bf16_x3_c4, 4)
+AGI_TC_GROUP_CLUSTER_KERNEL(agi_gemm_tc_bf16_x3_c8, 8)
+#undef AGI_TC_GROUP_CLUSTER_KERNEL
+
 // Single GEMM over packed operands, split-K slabs as in agi_gemm_tc_*.
 #define AGI_TC_PACKED_KERNEL(NAME, TYPE, FP8)                                                                         \
   extern "C" __global__ void __launch_bounds__(tc::kThreads, 1)                                                      \

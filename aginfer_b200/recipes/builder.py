@@ -182,7 +182,8 @@ FA_HEAD_DIMS = (48, 64, 80, 128)   # compiled widths of agi_attention_fa_bf16_d*
 TC_CLUSTER_SIZES = {"bf16": (2, 3, 4, 6, 8), "e4m3": (2, 4, 8)}   # compiled cluster variants
 
 
-def tc_cluster_tiling(M: int, N: int, K: int, elem: int, dtype: str = "bf16") -> dict[str, int] | None:
+def tc_cluster_tiling(M: int, N: int, K: int, elem: int, dtype: str = "bf16",
+                      sizes: Sequence[int] | None = None) -> dict[str, int] | None:
     """Geometry of ``agi_gemm_tc_*_c{C}``: the largest compiled cluster size that keeps all CTAs in one wave
     (n_tiles * C <= 148) and leaves every slice at least two K blocks."""
     if M > 64 or (K * elem) % 128:
@@ -190,7 +191,7 @@ def tc_cluster_tiling(M: int, N: int, K: int, elem: int, dtype: str = "bf16") ->
     TN = ceil_div(M, 16) * 16
     n_tiles = ceil_div(N, 128)
     k_blocks = K * elem // 128
-    usable = [c for c in TC_CLUSTER_SIZES[dtype] if n_tiles * c <= SM_COUNT and k_blocks >= 2 * c]
+    usable = [c for c in (sizes or TC_CLUSTER_SIZES[dtype]) if n_tiles * c <= SM_COUNT and k_blocks >= 2 * c]
     if not usable:
         return None
     cluster = max(usable)
@@ -505,12 +506,14 @@ class RecipeBuilder:
     def attention(self, q: Pointer, k: Pointer, v: Pointer, o: Pointer, *, q_rows: int, kv_rows: int, q_heads: int,
                   kv_heads: int, head_dim: int, q_stride: int, k_stride: int, v_stride: int, o_stride: int,
                   mask: str = "none", mask_arg: int = 0, scale: float | None = None,
-                  algorithm: str = "auto", amax: Pointer | None = None, kv_static: bool = False) -> None:
+                  algorithm: str = "auto", amax: Pointer | None = None, kv_static: bool = False,
+                  kv_static_rows: int | None = None) -> None:
         """``amax`` (a ``counter()`` slot; head widths 80 and 128, streaming tensor-core kernel only): the kernel
         also leaves max |o| there for a following ``quantize_e4m3(..., amax=)``.
         ``kv_static``: keys and values were written before the last ``agi_add_rows_bf16`` launch of the profile
         (which releases its successors only after its own wait), not by the launches since; the few-query-rows
-        kernel then requests them before its grid-dependency wait."""
+        kernel then requests them before its grid-dependency wait.  ``kv_static_rows``: only that many leading rows
+        (the prefix of a KV cache whose tail the previous launches just wrote)."""
         assert head_dim <= 128 and head_dim % 2 == 0 and q_heads % kv_heads == 0
         mode = {"none": 0, "causal": 1, "block": 2}[mask]
         args = [q, k, v, o, U32(q_rows), U32(kv_rows), U32(q_heads), U32(kv_heads), U32(head_dim), U32(q_stride),
@@ -529,9 +532,19 @@ class RecipeBuilder:
                 and mma_smem <= ATTN_SMEM_BUDGET and algorithm in ("auto", "mma")):
             # few query rows: one block per head, tensor-core scores and P.V
             if kv_static:
-                args = args[:14] + [U32(mode | 0x100), args[15]]
+                args = args[:14] + [U32(mode | 0x100 | (min(kv_static_rows or 0, 0xffff) << 16)), args[15]]
             self.launch("agi_attention_mma_bf16", (q_heads, ceil_div(q_rows, 16), 1), (256, 1, 1), args, shared_bytes=mma_smem,
                         op=f"attention_{mask}", algorithm="mma_key_split" + ("_early_kv" if kv_static else ""))
+            return
+        wide_smem = max(2 * kv16 * (head_dim + 8) * 2, 8 * 16 * (head_dim + 2) * 4)
+        if (aligned and q_rows <= 64 and 64 < head_dim <= 128 and head_dim % 16 == 0 and q_stride % 2 == 0 and o_stride % 2 == 0
+                and wide_smem <= ATTN_SMEM_BUDGET and amax is None and algorithm in ("auto", "mma")):
+            # few query rows, wide heads: the streaming kernel would give each of a handful of warps every key
+            if kv_static:
+                args = args[:14] + [U32(mode | 0x100 | (min(kv_static_rows or 0, 0xffff) << 16)), args[15]]
+            self.launch("agi_attention_mma_bf16_d128", (q_heads, ceil_div(q_rows, 16), 1), (256, 1, 1), args,
+                        shared_bytes=wide_smem, op=f"attention_{mask}",
+                        algorithm="mma_key_split_d128" + ("_early_kv" if kv_static else ""))
             return
         # streaming tensor-core kernel: 4, 2 or 1 warps (64, 32 or 16 query rows) per block, the most rows that still
         # give the grid about one block per SM
@@ -751,6 +764,16 @@ class RecipeBuilder:
             else:
                 args += [dummy, dummy, dummy, dummy, U32(0), U32(0)]
         grid_x = sum(ceil_div(p[4], 128) for p in parts)
+        if dtype == "bf16" and not packed and M <= 64:
+            # few tokens: too few tiles to fill the SMs, so the K slices of every tile form a cluster (as `cluster`
+            # does for one matrix) and the projections that share the activations still share the launch
+            c = tc_cluster_tiling(M, 128 * grid_x, K, elem, dtype, sizes=(2, 4, 8))
+            if c is not None:
+                args[7:9] = [U32(c["TN"]), U32(c["stages"])]
+                self.launch(f"agi_gemm_tc_bf16_x3_c{c['cluster']}", (grid_x, 1, c["cluster"]), (160, 1, 1), args,
+                            shared_bytes=c["shared_bytes"], op="gemm_bf16_group",
+                            algorithm=f"tcgen05_128x{c['TN']}_s{c['stages']}_cluster{c['cluster']}_x{len(parts)}")
+                return
         self.launch(f"agi_gemm_tcp_{dtype}_x3" if packed else f"agi_gemm_tc_{dtype}_x3", (grid_x, t["m_tiles"], 1),
                     (160, 1, 1), args, shared_bytes=t["shared_bytes"], op=f"gemm_{dtype}_group" + ("_packed" if packed else ""),
                     algorithm=f"tcgen05_{'bulk_' if packed else ''}128x{t['TN']}_s{t['stages']}_x{len(parts)}")

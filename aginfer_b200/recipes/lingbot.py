@@ -118,6 +118,16 @@ def build_recipe(cfg: EpisodeConfig, weights, packed: bool = False, trace: bool 
             bias = Weight(f"{name}.bias") if f"{name}.bias" in weights else None
             r.gemm(x, Weight(f"{name}.weight"), y, M, N, K, bias=bias, **kw)
 
+        def group(x, parts, M, K):
+            """Projections that share their input as one launch: ``parts`` = (name, y, N, ldy)."""
+            biased = {f"{name}.bias" in weights for name, *_ in parts}
+            if len(biased) != 1 or K % 64:          # mixed bias / odd K: one launch each
+                for name, y, N, ldy in parts:
+                    lin(x, name, y, M, N, K, ldy=ldy)
+                return
+            r.gemm_group(x, [(Weight(f"{name}.weight"), Weight(f"{name}.bias") if True in biased else None, None, y, N, ldy)
+                             for name, y, N, ldy in parts], M, K)
+
         # ---- once per episode: conditioning vectors of every step, latent, K/V of the prefix ----
         t_sin, t_hid, cond, s_pad, s_emb = (r.alloc(S * cfg.time_dim * BF), r.alloc(S * H * BF), r.alloc(S * H * BF),
                                             r.alloc(PAD * BF), r.alloc(H * BF))
@@ -154,18 +164,19 @@ def build_recipe(cfg: EpisodeConfig, weights, packed: bool = False, trace: bool 
                 k_rows = kcat + (j * keys + prefix) * KV * BF
                 v_rows = vcat + (j * keys + prefix) * KV * BF
                 r.rmsnorm(seq, Weight(f"{l}.input_layernorm.weight"), hn, T, H, bb.eps)
-                lin(hn, f"{l}.self_attn.q_proj", q_buf, T, H, H)
-                lin(hn, f"{l}.self_attn.k_proj", k_rows, T, KV, H)
-                lin(hn, f"{l}.self_attn.v_proj", v_rows, T, KV, H)
+                group(hn, [(f"{l}.self_attn.q_proj", q_buf, H, H), (f"{l}.self_attn.k_proj", k_rows, KV, KV),
+                           (f"{l}.self_attn.v_proj", v_rows, KV, KV)], T, H)
                 r.rope(q_buf, T, cfg.e_heads, D, H, bb.theta, pos_offset=pos0)
                 r.rope(k_rows, T, cfg.e_kv_heads, D, KV, bb.theta, pos_offset=pos0)
                 r.attention(q_buf, kcat + j * keys * KV * BF, vcat + j * keys * KV * BF, att, q_rows=T, kv_rows=keys,
                             q_heads=cfg.e_heads, kv_heads=cfg.e_kv_heads, head_dim=D, q_stride=H, k_stride=KV,
-                            v_stride=KV, o_stride=H, mask="none")
+                            v_stride=KV, o_stride=H, mask="none",
+                            # the prefix rows were copied in once per episode, before this step's conditioning add (a
+                            # launch that releases its successors only after its own wait); the tail is this layer's
+                            kv_static=True, kv_static_rows=prefix)
                 lin(att, f"{l}.self_attn.o_proj", seq2, T, H, H, residual=seq)
                 r.rmsnorm(seq2, Weight(f"{l}.post_attention_layernorm.weight"), hn, T, H, bb.eps)
-                lin(hn, f"{l}.mlp.gate_proj", gu, T, I, H, ldy=2 * I)
-                lin(hn, f"{l}.mlp.up_proj", gu + I * BF, T, I, H, ldy=2 * I)
+                group(hn, [(f"{l}.mlp.gate_proj", gu, I, 2 * I), (f"{l}.mlp.up_proj", gu + I * BF, I, 2 * I)], T, H)
                 r.swiglu(gu, gu + I * BF, act, T, I, 2 * I)
                 lin(act, f"{l}.mlp.down_proj", seq, T, H, I, residual=seq2)
             r.rmsnorm(seq, Weight(f"{E}.norm.weight"), hn, T, H, bb.eps)

@@ -148,6 +148,27 @@ def test_attention(tmp_path, case, algorithm):
     assert ops.max_rel_err(got["o"], want.reshape(sq, -1)) < MAX_REL
 
 
+@pytest.mark.parametrize("case,static_rows", [((17, 300, 32, 32, 48, "none", 0), None), ((50, 306, 8, 4, 128, "causal", 256), 256),
+                                              ((50, 306, 8, 4, 128, "none", 0), 250), ((64, 40, 4, 2, 96, "none", 0), 16),
+                                              ((17, 17, 32, 32, 48, "none", 0), 5)], ids=lambda c: str(c).replace(" ", ""))
+def test_attention_with_keys_requested_ahead_of_the_dependency_wait(tmp_path, case, static_rows):
+    """Few query rows, keys / values (or a leading part of them) declared static: the kernel requests those rows before
+    its grid-dependency wait.  Here they are profile inputs, so any split must give the result of the plain call."""
+    sq, skv, hq, hkv, d, mask, arg = case
+    q, k, v = randn(sq, hq * d, seed=9), randn(skv, hkv * d, seed=10), randn(skv, hkv * d, seed=11)
+
+    def body(r):
+        for name, kw in (("o_plain", {}), ("o_early", {"kv_static": True, "kv_static_rows": static_rows})):
+            r.attention(Tensor("q"), Tensor("k"), Tensor("v"), Tensor(name), q_rows=sq, kv_rows=skv, q_heads=hq, kv_heads=hkv,
+                        head_dim=d, q_stride=hq * d, k_stride=hkv * d, v_stride=hkv * d, o_stride=hq * d, mask=mask,
+                        mask_arg=arg, **kw)
+
+    got, _ = run_recipe(tmp_path, {}, {"q": q, "k": k, "v": v}, {"o_plain": (BF, (sq, hq * d)), "o_early": (BF, (sq, hq * d))}, body)
+    want = ops.attention(q.view(sq, hq, d), k.view(skv, hkv, d), v.view(skv, hkv, d), mask=mask, mask_arg=arg)
+    assert torch.equal(got["o_plain"], got["o_early"])
+    assert ops.max_rel_err(got["o_early"], want.reshape(sq, -1)) < MAX_REL
+
+
 FA_CASES = [
     (288, 288, 16, 2, 128, "causal", 0),     # decoder prefill: grouped-query, 4.5 key tiles
     (512, 512, 16, 16, 80, "block", 64),     # vision windows
@@ -315,6 +336,9 @@ def test_gemm_tcgen05_wide(tmp_path, case):
 
 
 @pytest.mark.parametrize("dtype,M,K,widths", [("e4m3", 288, 2048, (2048, 256, 256)), ("bf16", 300, 512, (1000, 72)),
+                                              # up to 64 tokens in bf16: K slices of every tile in a cluster (c8, c2, c4)
+                                              ("bf16", 50, 1024, (1024, 512, 512)), ("bf16", 50, 1024, (4096, 4096)),
+                                              ("bf16", 17, 1536, (1536, 1000, 520)),
                                               ("e4m3", 512, 1280, (3456, 3456)), ("bf16", 17, 128, (128,))])
 def test_gemm_group(tmp_path, dtype, M, K, widths):
     """Q | K | V style: several weight matrices over one activation matrix in one tensor-core launch."""

@@ -31,7 +31,9 @@ def test_full_size_episode_compiles_to_a_plan():
     kinds = collections.Counter(l["kernel"] for l in launches)
     assert kinds["agi_euler_step"] == cfg.steps
     assert kinds["agi_attention_fa_amax_bf16_d128"] == 28          # backbone: feeds an FP8 quantisation
-    assert kinds["agi_attention_fa_bf16_d128"] == 18 * 10          # expert: bf16 all the way
+    assert kinds["agi_attention_mma_bf16_d128"] == 18 * 10         # expert: 50 query rows, keys split over warps
+    # the expert's projections that share an input share a launch: Q | K | V (cluster of 8) and gate | up (of 2)
+    assert kinds["agi_gemm_tc_bf16_x3_c8"] == 18 * 10 and kinds["agi_gemm_tc_bf16_x3_c2"] == 18 * 10
     compiled = planfmt.compile_execution_plan(recipe.plan(), CudaArch.SM100, weight_size=recipe.weight_bytes)
     assert compiled.input_names == ("pixels", "input_ids", "positions", "state", "noise")
     assert "actions" in compiled.output_names
