@@ -25,6 +25,27 @@ extern "C" __global__ void agi_rope_bf16(bf16* x, unsigned rows, unsigned heads,
   }
 }
 
+// The same over two tensors in one launch (queries and the new keys of a decode step live in different buffers):
+// heads [0, heads0) are x0's, heads [heads0, heads0 + heads1) are x1's.
+extern "C" __global__ void agi_rope_pair_bf16(bf16* x0, unsigned heads0, unsigned row_stride0, bf16* x1, unsigned heads1,
+                                               unsigned row_stride1, unsigned rows, unsigned head_dim, float log2_theta,
+                                               unsigned pos_offset) {
+  grid_dependency_wait();
+  const unsigned half = head_dim / 2, heads = heads0 + heads1;
+  const unsigned total = rows * heads * half;
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const unsigned pair = i % half, head = (i / half) % heads, row = i / (half * heads);
+    const float inv_freq = exp2f(-log2_theta * (2.f * float(pair) / float(head_dim)));
+    float s, c;
+    sincosf(float(row + pos_offset) * inv_freq, &s, &c);
+    bf16* p = head < heads0 ? x0 + size_t(row) * row_stride0 + head * head_dim + pair
+                            : x1 + size_t(row) * row_stride1 + (head - heads0) * head_dim + pair;
+    const float a = __bfloat162float(p[0]), b = __bfloat162float(p[half]);
+    p[0] = __float2bfloat16_rn(a * c - b * s);
+    p[half] = __float2bfloat16_rn(b * c + a * s);
+  }
+}
+
 // Multimodal RoPE: three position streams (temporal, height, width) given as int32
 // pos[3][rows]; rotary pair i takes its position from stream 0 for i < s0, stream 1 for
 // i < s0 + s1, else stream 2 (sections (16, 24, 24) for head_dim 128).  `ladder` = rotary pairs per frequency

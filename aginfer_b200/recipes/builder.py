@@ -493,6 +493,14 @@ class RecipeBuilder:
                     [x, U32(rows), U32(heads), U32(head_dim), U32(row_stride), F32(math.log2(theta)), U32(pos_offset)],
                     op="rope")
 
+    def rope_pair(self, x0: Pointer, heads0: int, row_stride0: int, x1: Pointer, heads1: int, row_stride1: int,
+                  rows: int, head_dim: int, theta: float, pos_offset: int = 0) -> None:
+        """``rope`` over two tensors (queries and new keys in separate buffers) as one launch."""
+        work = rows * (heads0 + heads1) * head_dim // 2
+        self.launch("agi_rope_pair_bf16", (grid_for(work), 1, 1), (256, 1, 1),
+                    [x0, U32(heads0), U32(row_stride0), x1, U32(heads1), U32(row_stride1), U32(rows), U32(head_dim),
+                     F32(math.log2(theta)), U32(pos_offset)], op="rope")
+
     def mrope(self, x: Pointer, positions: Pointer, rows: int, heads: int, head_dim: int, row_stride: int,
               theta: float, sections: Sequence[int], ladder: int | None = None) -> None:
         """``ladder``: rotary pairs per frequency ladder (pair i turns at theta^(-(i mod ladder) / ladder));

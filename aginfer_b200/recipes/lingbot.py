@@ -166,8 +166,7 @@ def build_recipe(cfg: EpisodeConfig, weights, packed: bool = False, trace: bool 
                 r.rmsnorm(seq, Weight(f"{l}.input_layernorm.weight"), hn, T, H, bb.eps)
                 group(hn, [(f"{l}.self_attn.q_proj", q_buf, H, H), (f"{l}.self_attn.k_proj", k_rows, KV, KV),
                            (f"{l}.self_attn.v_proj", v_rows, KV, KV)], T, H)
-                r.rope(q_buf, T, cfg.e_heads, D, H, bb.theta, pos_offset=pos0)
-                r.rope(k_rows, T, cfg.e_kv_heads, D, KV, bb.theta, pos_offset=pos0)
+                r.rope_pair(q_buf, cfg.e_heads, H, k_rows, cfg.e_kv_heads, KV, T, D, bb.theta, pos_offset=pos0)
                 r.attention(q_buf, kcat + j * keys * KV * BF, vcat + j * keys * KV * BF, att, q_rows=T, kv_rows=keys,
                             q_heads=cfg.e_heads, kv_heads=cfg.e_kv_heads, head_dim=D, q_stride=H, k_stride=KV,
                             v_stride=KV, o_stride=H, mask="none",

@@ -104,6 +104,27 @@ def test_rope_1d(tmp_path):
     assert ops.max_rel_err(got["y"], want.view(rows, -1)) < 1e-2
 
 
+def test_rope_over_two_tensors_in_one_launch_matches_two_launches(tmp_path):
+    rows, hq, hk, d, offset = 50, 8, 4, 128, 88    # the action expert's queries and new keys
+    q, k = randn(rows, hq * d, seed=7), randn(rows, hk * d, seed=8)
+    from aginfer_b200.recipes import U32
+
+    def body(r):
+        for src, dst, width in (("q", "q1", hq * d), ("q", "q2", hq * d), ("k", "k1", hk * d), ("k", "k2", hk * d)):
+            r.launch("agi_copy_rows_bf16", (200, 1, 1), (256, 1, 1),
+                     [Tensor(src), Tensor(dst), U32(rows), U32(width), U32(width), U32(width)])
+        r.rope(Tensor("q1"), rows, hq, d, hq * d, 1e6, pos_offset=offset)
+        r.rope(Tensor("k1"), rows, hk, d, hk * d, 1e6, pos_offset=offset)
+        r.rope_pair(Tensor("q2"), hq, hq * d, Tensor("k2"), hk, hk * d, rows, d, 1e6, pos_offset=offset)
+
+    got, _ = run_recipe(tmp_path, {}, {"q": q, "k": k}, {"q1": (BF, q.shape), "q2": (BF, q.shape), "k1": (BF, k.shape),
+                                                         "k2": (BF, k.shape)}, body)
+    # two compilations of the same arithmetic may contract multiply-adds differently: equal to rounding, not bit for bit
+    assert ops.max_rel_err(got["q2"], got["q1"].float()) < 5e-3 and ops.max_rel_err(got["k2"], got["k1"].float()) < 5e-3
+    assert ops.max_rel_err(got["q2"], ops.rope(q.view(rows, hq, d), 1e6, offset).reshape(rows, -1)) < 1e-2
+    assert ops.max_rel_err(got["k2"], ops.rope(k.view(rows, hk, d), 1e6, offset).reshape(rows, -1)) < 1e-2
+
+
 def test_mrope_sections(tmp_path):
     from aginfer_b200.recipes import U32
     rows, heads, d = 64, 4, 128
