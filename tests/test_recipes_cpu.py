@@ -80,3 +80,43 @@ def test_cubin_exports_every_kernel_the_builder_names():
                  "agi_layernorm_bf16", "agi_rope_bf16", "agi_mrope_bf16", "agi_attention_bf16", "agi_swiglu_bf16",
                  "agi_gemm_simt_bf16", "agi_gemm_simt_e4m3", "agi_euler_step"):
         assert name.encode() + b"\0" in blob, name
+
+
+def _kernels(body, weights=None):
+    weights = weights or {"w": torch.zeros(4096, 4096, dtype=torch.bfloat16), "w2": torch.zeros(4096, 1024, dtype=torch.bfloat16)}
+    r = RecipeBuilder(describe(weights))
+    r.begin_profile("default", [io("x", "BF16", [64, 8192])], [io("y", "BF16", [64, 8192])])
+    body(r)
+    return r.plan()["shape_dispatch"][0]["launches"][1:]      # without the prologue
+
+
+def test_launch_geometry_choices_for_few_tokens():
+    """The builder's choices that the action head and the action expert rely on, as launch records."""
+    from aginfer_b200.recipes.builder import stream_splits, stream_tiling, tc_cluster_tiling
+    # a long K becomes four rings side by side in a cluster; a K that one ring covers in <= 4 chunks stays whole
+    assert stream_splits(17, 1536, 6144, 2) == 4 and stream_splits(17, 6144, 1536, 2) == 1
+    assert stream_splits(50, 1024, 4096, 2) == 1 and stream_splits(17, 1536, 6144, 1) == 1      # > 32 tokens; FP8
+    t = stream_tiling(17, 1536, 6144, 2, splits=4)
+    assert (t["rows"], t["grid"], t["slots"]) == (16, 96, 2) and 3 * t["shared_bytes"] <= 227 * 1024
+    x, y = Tensor("x"), Tensor("y")
+    (down,) = _kernels(lambda r: r.gemm(x, Weight("w"), y, 17, 1536, 4096 + 2048, ldx=8192))
+    assert down["kernel"] == "agi_gemm_stream_bf16_t3_k4" and down["grid"] == [96, 1, 4]
+    # projections that share their input: one grouped launch, K slices of every tile in a cluster when tokens are few
+    parts = lambda r, n: [(Weight("w2"), None, None, y, n, 8192), (Weight("w2") + n * 2048, None, None, r.alloc(64 * 8192 * 2), n, 8192)]
+    (few,) = _kernels(lambda r: r.gemm_group(x, parts(r, 1024), 50, 1024))
+    (many,) = _kernels(lambda r: r.gemm_group(x, parts(r, 1024), 300, 1024))
+    assert few["kernel"] == "agi_gemm_tc_bf16_x3_c8" and few["grid"] == [16, 1, 8]
+    assert many["kernel"] == "agi_gemm_tc_bf16_x3" and many["grid"][2] == 1
+    assert tc_cluster_tiling(50, 8192, 1024, 2, sizes=(2, 4, 8))["cluster"] == 2
+    # few query rows: the key-split kernel, by head width; static keys / values are flagged in the mask word
+    kw = dict(q_rows=50, kv_rows=306, q_heads=8, kv_heads=4, q_stride=1024, k_stride=512, v_stride=512, o_stride=1024)
+    (wide,) = _kernels(lambda r: r.attention(x, x, x, y, head_dim=128, kv_static=True, kv_static_rows=256, **kw))
+    assert wide["kernel"] == "agi_attention_mma_bf16_d128" and wide["grid"] == [8, 4, 1]
+    assert wide["shared_bytes"] == 2 * 320 * 136 * 2 and wide["arguments"][14] == {"scalar_u32": 0x100 | (256 << 16)}
+    kw.update(q_rows=17, kv_rows=300, q_heads=32, kv_heads=32, q_stride=1536, k_stride=1536, v_stride=1536, o_stride=1536)
+    (narrow,) = _kernels(lambda r: r.attention(x, x, x, y, head_dim=48, **kw))
+    assert narrow["kernel"] == "agi_attention_mma_bf16" and narrow["arguments"][14] == {"scalar_u32": 0}
+    (streaming,) = _kernels(lambda r: r.attention(x, x, x, y, head_dim=128, **{**kw, "q_rows": 288, "kv_rows": 288, "q_heads": 16,
+                                                                                "kv_heads": 2, "q_stride": 2048, "k_stride": 256,
+                                                                                "v_stride": 256, "o_stride": 2048}))
+    assert streaming["kernel"].startswith("agi_attention_fa_bf16_d128")
