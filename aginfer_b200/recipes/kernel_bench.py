@@ -25,7 +25,8 @@ GEMM_SHAPES = {"gemm_q": (D, D), "gemm_fc1": (MLP, D), "gemm_fc2": (D, MLP),
                "gemm_1024x1024": (1024, 1024), "gemm_512x1024": (512, 1024), "gemm_4096x1024": (4096, 1024),
                "gemm_1024x4096": (1024, 4096),     # action expert
                "gemm_3584x3584": (3584, 3584), "gemm_18944x3584": (18944, 3584), "gemm_3584x18944": (3584, 18944)}
-CASES = ("empty", "layernorm", "attn_self", "attn_cross", "attn_prefill", "attn_vision", "group_qkv", "batch_kv",
+CASES = ("empty", "layernorm", "attn_self", "attn_cross", "attn_prefill", "attn_vision", "attn_expert", "group_qkv",
+         "group_expert_qkv", "batch_kv",
          "quantize_packed", "rmsnorm_amax", "mrope", "swiglu_amax", "dit_blocks", *GEMM_SHAPES)
 
 
@@ -56,6 +57,11 @@ def build(case: str, tactic: str, reps: int, tokens: int, stages: int = 4, dtype
                 w = (torch.randn(n, 2048, generator=g) * 0.02).clamp(-0.08, 0.08).mul(448 / 0.08).to(torch.float8_e4m3fn)
                 weights[f"l{l}.{part}"] = pack_kblock_swizzled(w) if packed else w
         weights["w_scale"] = torch.tensor(0.08 / 448, dtype=torch.float32)
+    if case == "group_expert_qkv":
+        g = torch.Generator().manual_seed(0)
+        for l in range(LAYERS):
+            for part, n in (("q", 1024), ("k", 512), ("v", 512)):
+                weights[f"l{l}.{part}"] = (torch.randn(n, 1024, generator=g) * 0.02).to(torch.bfloat16)
     if case == "batch_kv":        # the action head's cross-attention K / V projections: 16 x (1536 x 2048) bf16, one launch
         g = torch.Generator().manual_seed(0)
         for l in range(LAYERS):
@@ -78,6 +84,14 @@ def build(case: str, tactic: str, reps: int, tokens: int, stages: int = 4, dtype
             r.attention(q, kbuf, vbuf, y, q_rows=tokens, kv_rows=kv_rows, q_heads=32, kv_heads=32, head_dim=48,
                         q_stride=D, k_stride=D, v_stride=D, o_stride=D,
                         algorithm=tactic if tactic in ("warp_per_row", "keys_in_smem", "mma") else "auto")
+        elif case == "attn_expert":       # action expert: `tokens` queries over a 256-row prefix + themselves, 8 / 4 heads of 128
+            r.attention(q, kbuf, vbuf, y, q_rows=tokens, kv_rows=256 + tokens, q_heads=8, kv_heads=4, head_dim=128,
+                        q_stride=1024, k_stride=512, v_stride=512, o_stride=1024,
+                        algorithm=tactic if tactic in ("warp_per_row", "keys_in_smem", "mma") else "auto")
+        elif case == "group_expert_qkv":  # action expert Q | K | V (1024 | 512 | 512 rows, K = 1024, bf16) as one launch
+            r.gemm_group(x, [(Weight(f"l{i % LAYERS}.q"), None, None, y, 1024, 2048),
+                             (Weight(f"l{i % LAYERS}.k"), None, None, y + 1024 * 2, 512, 2048),
+                             (Weight(f"l{i % LAYERS}.v"), None, None, y + 1536 * 2, 512, 2048)], tokens, 1024)
         elif case == "attn_prefill":      # decoder prefill: `tokens` causal rows, 16 query / 2 KV heads of 128
             r.attention(q, kbuf, vbuf, y, q_rows=tokens, kv_rows=tokens, q_heads=16, kv_heads=2, head_dim=128,
                         q_stride=2048, k_stride=256, v_stride=256, o_stride=2048, mask="causal")
